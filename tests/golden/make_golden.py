@@ -1,0 +1,238 @@
+"""Generate tests/golden/reference_vectors.npz from the reference's own CPU oracles.
+
+Run once, in a container that has the reference checkout (it cannot travel to
+the GPU box, so the vectors are committed):
+
+    REFERENCE_ROOT=/path/to/reference python tests/golden/make_golden.py
+
+It imports, unmodified, from the reference:
+  * ``_sdpa_reference_attention_sps``      src/modeling/tests/attention/triton/test_sps_attention.py:25-74
+  * ``_reference_persistent_key_window_attention``
+                                            src/modeling/tests/models/attention/test_persistent_key_window.py:14-51
+  * ``_pytorch_reference_attention``       src/modeling/tests/attention/triton/test_full_flash_attention.py:29-59
+  * ``_reference_q2_attention``            src/modeling/tests/models/attention/test_segmented_q2_attention.py:25-62
+  * ``masked_kv_attention`` (SDPA path)    src/modeling/models/utils/decode_attention.py:597-704
+  * ``window_score_mod_factory``           src/modeling/tests/_sliding_window_reference.py:15-34
+  * the eager cache update methods         src/modeling/models/reverse_sps/inference.py:137-167, :240-268
+    through the reference's own tiny Delayed-State test model.
+
+Every case stores its inputs (bf16/fp16 values widened to fp32, integer tensors
+as int64) next to the reference output so the tests need nothing but numpy.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+import sys
+
+sys.dont_write_bytecode = True
+REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+sys.path[:0] = [os.path.join(REF, "src"), REF]
+
+import numpy as np
+import torch
+
+from modeling.models.utils.decode_attention import KVSegment, masked_kv_attention
+from modeling.tests._sliding_window_reference import window_score_mod_factory
+from modeling.tests.attention.triton.test_full_flash_attention import _pytorch_reference_attention
+from modeling.tests.attention.triton.test_sps_attention import _sdpa_reference_attention_sps
+from modeling.tests.models.attention.test_persistent_key_window import (
+    _reference_persistent_key_window_attention,
+)
+from modeling.tests.models.attention.test_segmented_q2_attention import _reference_q2_attention
+
+OUT = {}
+
+
+def put(name, t):
+    """Store one array; floats that are exactly bf16-representable are stored as
+    their 16-bit patterns under ``<name>__bf16`` (tests/golden/loader.py widens them)."""
+    if isinstance(t, torch.Tensor):
+        t = t.detach().cpu()
+        if t.is_floating_point():
+            t = t.float()
+            if t.numel() > 64 and torch.equal(t.bfloat16().float(), t):
+                OUT[name + "__bf16"] = t.bfloat16().view(torch.int16).numpy().view(np.uint16)
+                return
+            t = t.numpy()
+        else:
+            t = t.long().numpy()
+    OUT[name] = np.asarray(t)
+
+
+def geometric_docs(batch, t, mean, seed):
+    rng = np.random.default_rng(seed)
+    rows = []
+    for _ in range(batch):
+        ids, d = [], 0
+        while len(ids) < t:
+            ids += [d] * int(rng.geometric(1.0 / mean))
+            d += 1
+        rows.append(ids[:t])
+    return torch.tensor(rows, dtype=torch.long).repeat_interleave(2, dim=1)
+
+
+def sps_cases():
+    # the reference's own kernel-parity case (test_sps_attention.py:77-131)
+    for tag, with_docs in (("nodoc", False), ("doc", True)):
+        torch.manual_seed(17)
+        b, h, t, d, w = 1, 2, 16, 64, 3
+        q, k, v = (torch.randn(b, h, 2 * t, d).bfloat16().float() for _ in range(3))
+        docs = None
+        if with_docs:
+            docs = torch.tensor([[0] * 6 + [1] * 8 + [2] * 2]).repeat_interleave(2, dim=1)
+            put(f"sps_{tag}_docs", docs)
+        put(f"sps_{tag}_q", q), put(f"sps_{tag}_k", k), put(f"sps_{tag}_v", v)
+        put(f"sps_{tag}_w", np.int64(w))
+        put(f"sps_{tag}_out", _sdpa_reference_attention_sps(q, k, v, w, documents_idx_BxT=docs))
+    # ragged / odd sizes: 2T in {8, 24, 200}, several windows, packed documents
+    for n, w, mean, seed in ((8, 1, 3, 1), (24, 2, 5, 2), (200, 7, 30, 3), (384, 64, 60, 4)):
+        g = torch.Generator().manual_seed(100 + n)
+        q, k, v = (torch.randn(2, 2, n, 64, generator=g).bfloat16().float() for _ in range(3))
+        docs = geometric_docs(2, n // 2, mean, seed)
+        tag = f"sps_n{n}"
+        put(f"{tag}_q", q), put(f"{tag}_k", k), put(f"{tag}_v", v), put(f"{tag}_docs", docs)
+        put(f"{tag}_w", np.int64(w))
+        put(f"{tag}_out", _sdpa_reference_attention_sps(q, k, v, w, documents_idx_BxT=docs))
+    # the CPU-runnable benchmark shape: [2,8,512,64] fp32, w=64, documents ~ Geometric(mean 100);
+    # inputs are regenerated from the seed by the test, only 2 heads of output are kept
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(2, 8, 512, 64, generator=g) for _ in range(3))
+    docs = geometric_docs(2, 256, 100, 0)
+    out = _sdpa_reference_attention_sps(q, k, v, 64, documents_idx_BxT=docs)
+    put("sps_cfg0_docs", docs)
+    put("sps_cfg0_q_checksum", q.double().sum() + 2 * k.double().sum() + 3 * v.double().sum())
+    put("sps_cfg0_out_h0h5", out[:, [0, 5]])
+
+
+def persistent_window_cases():
+    # test_persistent_key_window.py:54-98, both parities (fp16 inputs)
+    for rem in (0, 1):
+        torch.manual_seed(0)
+        q = torch.randn(1, 1, 8, 64).half().float()
+        k, v = torch.randn_like(q).half().float(), torch.randn_like(q).half().float()
+        out = _reference_persistent_key_window_attention(
+            q, k, v, persistent_key_window=1, persistent_key_remainder=rem, temporary_key_window=8)
+        put(f"pkw{rem}_q", q), put(f"pkw{rem}_k", k), put(f"pkw{rem}_v", v), put(f"pkw{rem}_out", out)
+    # a larger one with a real temporary window as well
+    for rem in (0, 1):
+        g = torch.Generator().manual_seed(7 + rem)
+        q, k, v = (torch.randn(1, 2, 96, 64, generator=g).bfloat16().float() for _ in range(3))
+        out = _reference_persistent_key_window_attention(
+            q, k, v, persistent_key_window=5, persistent_key_remainder=rem, temporary_key_window=2)
+        put(f"pkwL{rem}_q", q), put(f"pkwL{rem}_k", k), put(f"pkwL{rem}_v", v), put(f"pkwL{rem}_out", out)
+
+
+def full_cases():
+    for n, d, seed in ((128, 64, 5), (200, 128, 6)):
+        g = torch.Generator().manual_seed(seed)
+        q, k, v = (torch.randn(2, 2, n, d, generator=g).bfloat16().float() for _ in range(3))
+        docs = geometric_docs(2, n, 40, seed)[:, ::2].contiguous()
+        tag = f"full_n{n}"
+        put(f"{tag}_q", q), put(f"{tag}_k", k), put(f"{tag}_v", v), put(f"{tag}_docs", docs)
+        put(f"{tag}_out", _pytorch_reference_attention(q, k, v, 1.0 / math.sqrt(d), docs))
+        put(f"{tag}_out_nodoc", _pytorch_reference_attention(q, k, v, 1.0 / math.sqrt(d), None))
+
+
+def decode_cases():
+    # test_segmented_q2_attention.py:65-117 on CPU tensors
+    for tag in ("shared", "empty"):
+        torch.manual_seed(123)
+        bsz, nh, hd = 2, 3, 16
+        q = torch.randn(bsz, 2, nh, hd).bfloat16()
+        k0 = torch.randn(bsz, nh, 7, hd).bfloat16()
+        v0 = torch.randn_like(k0)
+        k1 = torch.randn(bsz, nh, 11, hd).bfloat16()
+        v1 = torch.randn_like(k1)
+        if tag == "empty":
+            len0, cap0 = torch.zeros((bsz,), dtype=torch.long), 0
+        else:
+            len0, cap0 = torch.tensor([2, 5]), 5
+        len1 = torch.tensor([[1, 3, 6], [2, 4, 7]])
+        segs = [KVSegment(k0, v0, len0, max_len_cap=cap0), KVSegment(k1, v1, len1, max_len_cap=8)]
+        cnk = torch.randn(bsz, nh, hd).bfloat16()
+        cnv, cpk, cpv = torch.randn_like(cnk), torch.randn_like(cnk), torch.randn_like(cnk)
+        out = _reference_q2_attention(q, segs, current_normal_k_BxHxD=cnk, current_normal_v_BxHxD=cnv,
+                                      current_predict_k_BxHxD=cpk, current_predict_v_BxHxD=cpv)
+        for nm, t in (("q", q), ("k0", k0), ("v0", v0), ("k1", k1), ("v1", v1), ("len0", len0),
+                      ("len1", len1), ("cnk", cnk), ("cnv", cnv), ("cpk", cpk), ("cpv", cpv),
+                      ("out", out)):
+            put(f"q2_{tag}_{nm}", t)
+        put(f"q2_{tag}_cap0", np.int64(cap0))
+        # the reference's own SDPA fallback, one query at a time, must agree with it
+        o0 = masked_kv_attention(q[:, 0].float(), segs, extra_kv=[(cnk, cnv)], attn_dtype=torch.float32)
+        o1 = masked_kv_attention(q[:, 1].float(), segs, extra_kv=[(cnk, cnv), (cpk, cpv)],
+                                 attn_dtype=torch.float32)
+        put(f"q2_{tag}_sdpa", torch.stack([o0, o1], dim=1))
+    # a q=1 case with three segments and head_dim 64 (Standard decode / stepwise prefill shape)
+    g = torch.Generator().manual_seed(9)
+    bsz, nh, hd = 3, 4, 64
+    q = torch.randn(bsz, nh, hd, generator=g).bfloat16()
+    segs, names = [], []
+    for i, (cap, per_head) in enumerate(((40, False), (9, True), (300, True))):
+        kk = torch.randn(bsz, nh, cap, hd, generator=g).bfloat16()
+        vv = torch.randn(bsz, nh, cap, hd, generator=g).bfloat16()
+        shape = (bsz, nh) if per_head else (bsz,)
+        ln = torch.randint(0, cap + 1, shape, generator=g)
+        segs.append(KVSegment(kk, vv, ln))
+        put(f"q1_k{i}", kk), put(f"q1_v{i}", vv), put(f"q1_len{i}", ln)
+    ek = torch.randn(bsz, nh, hd, generator=g).bfloat16()
+    ev = torch.randn(bsz, nh, hd, generator=g).bfloat16()
+    put("q1_q", q), put("q1_ek", ek), put("q1_ev", ev)
+    put("q1_out", masked_kv_attention(q.float(), [KVSegment(s.k.float(), s.v.float(), s.lengths) for s in segs],
+                                      extra_kv=[(ek.float(), ev.float())], attn_dtype=torch.float32))
+
+
+def visibility_cases():
+    # tests/models/reverse_sps/test_forward_efficient.py:130-156: which normal (even) keys a
+    # query sees under the odd-persistent rule, straight from the reference's score modifier
+    t = 5
+    for w in (0, 1, 2):
+        mod = window_score_mod_factory(window_size=w)
+        vis = np.zeros((2 * t, 2 * t), dtype=np.int64)
+        for qi in range(2 * t):
+            for ki in range(qi + 1):
+                s = mod(torch.tensor(0.0), torch.tensor(0), torch.tensor(0),
+                        torch.tensor(qi), torch.tensor(ki))
+                vis[qi, ki] = int(torch.isfinite(s))
+        put(f"vis_reverse_w{w}", vis)
+
+
+def kv_update_cases():
+    from modeling.tests.models.delayed_state.test_forward_efficient import _make_delayed_state_model
+    torch.manual_seed(11)
+    w, steps, bsz, max_tokens = 3, 7, 3, 8
+    model = _make_delayed_state_model(window_size=w)
+    nh = model.config.n_head
+    hd = model.config.hidden_size // nh
+    state = model._build_decode_state(batch_size=bsz, max_tokens=max_tokens, device=torch.device("cpu"),
+                                      attn_dtype=torch.float32)
+    seq = []
+    for step in range(steps):
+        kw, vw = torch.randn(bsz, nh, hd), torch.randn(bsz, nh, hd)
+        kr, vr = torch.randn(bsz, nh, hd), torch.randn(bsz, nh, hd)
+        active = torch.tensor([True, step % 3 != 1, step < 4])
+        model._update_normal_memory_unfused(state, 0, kw, vw, active)
+        model._update_predict_memory_unfused(state, 0, kr, vr, active)
+        seq.append((kw, vw, kr, vr, active.long()))
+    for i, nm in enumerate(("kw", "vw", "kr", "vr", "active")):
+        put(f"kvu_{nm}", torch.stack([s[i] for s in seq]))
+    put("kvu_window", np.int64(w))
+    put("kvu_nw_k", state.normal_window.k[0]), put("kvu_nw_v", state.normal_window.v[0])
+    put("kvu_nw_len", state.normal_window.len[0]), put("kvu_nw_pos", state.normal_window.pos[0])
+    put("kvu_br_k", state.predict_retained.k[0]), put("kvu_br_v", state.predict_retained.v[0])
+    put("kvu_br_len", state.predict_retained.len[0])
+
+
+if __name__ == "__main__":
+    with torch.no_grad():
+        sps_cases()
+        persistent_window_cases()
+        full_cases()
+        decode_cases()
+        visibility_cases()
+        kv_update_cases()
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
+    np.savez_compressed(path, **OUT)
+    print(f"wrote {path}: {len(OUT)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
