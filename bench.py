@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""Benchmark of the SPS attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of SPS prefill attention over the s-scale configuration
+([8, 12, 8192, 64] bf16, w = 64, packed documents ~ Geometric(mean 1000 tokens)); the headline
+metric is useful (unmasked) TFLOP/s.  The same run also times the segmented decode step
+(128 sequences, cache lengths U[512, 4096], ring 64, 16 heads x 64) and reports it under
+"decode" with its own HBM roofline.  With N > 1 (one process per GPU under torchrun) every rank
+runs the full per-GPU workload on its own shard of sequences: no collective on the data path,
+weak scaling, time = max over ranks.
+
+`--impl reference` times the reference's CPU formulation of the same math (dense additive
+mask + SDPA, restated in oracle/) on the host cores, on a bounded sample of the workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+PREFILL = "cfg1_s_scale"
+DECODE = "cfg2_segmented_decode"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+        self._period = period_s
+
+    def _loop(self):
+        nv = self._nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self._period)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "samples": len(self.samples), "reasons": sorted(self.reasons)}
+
+
+def dist_setup(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group(backend="nccl" if torch.cuda.is_available() else "gloo")
+    return world, rank, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def max_over_ranks(x: float, world: int, device) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def timed_steps(fn, steps, warmup, world, device):
+    """W untimed steps, then exactly K steps bracketed by barrier + synchronize; CUDA events on
+    the launching stream give the whole region and every launch.  Returns (region ms as max over
+    ranks, mean launch ms on this rank)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    barrier(world)
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    barrier(world)
+    torch.cuda.synchronize()
+    region = ev[0].elapsed_time(ev[-1])
+    per = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+    return max_over_ranks(region, world, device), float(np.mean(per))
+
+
+# ------------------------------------------------------------------------------------- ours
+
+def run_ours(args):
+    import sps_b200
+    from sps_b200 import workloads
+
+    world, rank, local = dist_setup(args.gpus)
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    peaks, peak_kind = load_peaks()
+    K, W = args.steps, max(args.warmup, 3)
+
+    # ---------------- prefill (headline)
+    wl = workloads.make_prefill(PREFILL, device, seed=rank)
+    out = torch.empty_like(wl.q)
+
+    def prefill_step():
+        sps_b200.prefill_attention(wl.q, wl.k, wl.v, wl.sm_scale, persistent_parity=0,
+                                   temporary_window=wl.window, documents_idx=wl.docs, out=out)
+
+    with ClockSampler(local) as clk:
+        region_ms, launch_ms = timed_steps(prefill_step, K, W, world, device)
+    sps_b200.check_device_status(device)
+    flops_all = wl.flops if world == 1 else _sum_over_ranks(wl.flops, world, device)
+    value = flops_all * K / (region_ms * 1e-3) / 1e12
+    achieved = wl.flops / (launch_ms * 1e-3) / 1e12
+    peak = float(peaks["bf16_tflops"])
+    B, H, N, D = wl.q.shape
+    result = {
+        "metric": "sps_prefill_useful_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": region_ms / K, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": f"{PREFILL}: SPS prefill attention [B={B},H={H},2T={N},D={D}] bf16, w={wl.window}, "
+                        "documents ~ Geometric(mean 1000 tokens), reference mask rule, per GPU",
+            "useful_gflop_per_step_per_gpu": wl.flops / 1e9,
+            "l2": f"inputs larger than L2: {4 * wl.q.numel() * 2 / 1e6:.0f} MB of Q/K/V/O per step vs 126 MB",
+            "parallelism": f"independent shards x{world}, no collective",
+        },
+        "clocks": clk.summary(),
+        "gpu_launches": 2 * K,      # document pre-pass + attention kernel per step
+        "roofline": {
+            "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak, "traffic": None,
+            "peak_source": f"{peak_kind} bf16 burst (kernel timed alone)",
+            "launch_ms": launch_ms,
+        },
+    }
+
+    # ---------------- end to end through the public API with host buffers
+    if not args.skip_e2e:
+        hq, hk, hv = (x.cpu().pin_memory() for x in (wl.q, wl.k, wl.v))
+        hdocs = wl.docs.cpu().pin_memory()
+        ho = torch.empty_like(hq).pin_memory()
+        dq, dk, dv = (torch.empty_like(wl.q) for _ in range(3))
+        ddocs = torch.empty_like(wl.docs)
+
+        def e2e_step():
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            ddocs.copy_(hdocs, non_blocking=True)
+            o = sps_b200.sps_sliding_attention(dq, dk, dv, wl.sm_scale, wl.window, documents_idx_BxT=ddocs)
+            ho.copy_(o, non_blocking=True)
+
+        ke = max(3, min(K, 20))
+        e2e_ms, _ = timed_steps(e2e_step, ke, 3, world, device)
+        result["e2e"] = {
+            "value": flops_all * ke / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "h2d_bytes_per_step": int(3 * hq.numel() * 2 + hdocs.numel() * 8),
+            "d2h_bytes_per_step": int(ho.numel() * 2), "steps": ke, "ms_per_step": e2e_ms / ke,
+        }
+        del hq, hk, hv, ho, dq, dk, dv
+
+    # ---------------- segmented decode step (second half of the metric)
+    if not args.skip_decode:
+        del wl, out
+        torch.cuda.empty_cache()
+        dw = workloads.make_decode(DECODE, device, seed=rank)
+        segs = [sps_b200.KVSegment(dw.ring_k, dw.ring_v, dw.ring_len, max_len_cap=dw.ring_k.shape[2]),
+                sps_b200.KVSegment(dw.cache_k, dw.cache_v, dw.cache_len, max_len_cap=dw.cache_k.shape[2])]
+
+        def decode_step():
+            sps_b200.segmented_q2_attention(
+                dw.q, segs, current_normal_k_BxHxD=dw.cur_k, current_normal_v_BxHxD=dw.cur_v,
+                current_predict_k_BxHxD=dw.pred_k, current_predict_v_BxHxD=dw.pred_v,
+                attn_dtype=torch.bfloat16)
+
+        d_region, d_launch = timed_steps(decode_step, K, W, world, device)
+        S = dw.q.shape[0]
+        gbs = dw.bytes / (d_launch * 1e-3) / 1e9
+        hbm = float(peaks["hbm_gbs"])
+        result["decode"] = {
+            "workload": f"{DECODE}: {S} sequences/GPU, cache lengths U[512,4096], ring 64, 16 heads x 64, "
+                        "2 queries per sequence, bf16 cache, per layer-step",
+            "tokens_per_s": world * S * K / (d_region * 1e-3), "ms_per_step": d_region / K,
+            "algorithmic_mb_per_step": dw.bytes / 1e6, "gpu_launches": 2 * K,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                         "traffic": None, "peak_source": f"{peak_kind} copy bandwidth", "launch_ms": d_launch},
+        }
+        sps_b200.check_device_status(device)
+
+    # ---------------- CPU baseline beside it (rank 0, single GPU runs only)
+    if world == 1 and not args.skip_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(budget_s=12.0)
+    if rank == 0:
+        print(json.dumps(result))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def _sum_over_ranks(x, world, device):
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+# -------------------------------------------------------------------------- CPU baseline
+
+def cpu_sample(n_heads: int):
+    """One bounded sample of the prefill workload on the host: batch row 0, the first `n_heads`
+    heads, full length (2T = 8192), through the dense-mask + SDPA formulation."""
+    from oracle import sps_oracle as orc
+    from sps_b200 import workloads
+    B, H, T, D, w, mean = workloads.PREFILL_CONFIGS[PREFILL]
+    docs = workloads.geometric_docs(B, T, mean, 0)[:1]
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(1, n_heads, 2 * T, D, generator=g) for _ in range(3))
+    flops = workloads.prefill_flops(workloads.useful_pairs(docs, w), n_heads, D)
+    dd = torch.from_numpy(docs)
+
+    def run():
+        return orc.prefill_attention_sdpa(q, k, v, 1.0 / np.sqrt(D), temporary_window=w, docs=dd)
+
+    return run, flops
+
+
+def cpu_baseline(budget_s: float):
+    torch.set_num_threads(os.cpu_count() or 1)
+    run, flops = cpu_sample(2)
+    run()                                   # warm-up
+    t0, n = time.perf_counter(), 0
+    while True:
+        run()
+        n += 1
+        if time.perf_counter() - t0 > budget_s or n >= 50:
+            break
+    dt = (time.perf_counter() - t0) / n
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{PREFILL} batch row 0, heads 0-1, full length 8192: dense additive mask + "
+                      f"torch SDPA fp32 (the reference's CPU formulation), {n} passes of {dt:.2f} s",
+            "seconds_per_pass": dt}
+
+
+def run_reference(args):
+    """The reference's CPU path for this workload on the host cores: rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    from sps_b200 import workloads
+    K, W = args.steps, args.warmup
+    run, flops = cpu_sample(1)
+    for _ in range(min(W, 2)):
+        run()
+    K = max(1, min(K, 20))
+    t0 = time.perf_counter()
+    for _ in range(K):
+        run()
+    dt = time.perf_counter() - t0
+    value = flops * K / dt / 1e12
+    B, H, T, D, w, _ = workloads.PREFILL_CONFIGS[PREFILL]
+    sample = f"{PREFILL} batch row 0, head 0, full length {2 * T} per step"
+    print(json.dumps({
+        "impl": "reference", "metric": "sps_prefill_useful_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": K, "warmup": min(W, 2), "ms_per_step": dt / K * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{PREFILL}: SPS prefill attention [B={B},H={H},2T={2 * T},D={D}], w={w}, "
+                               "documents ~ Geometric(mean 1000 tokens); CPU sample: " + sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample + ": dense additive mask + torch SDPA fp32 "
+                                            "(the reference's CPU formulation restated in oracle/)"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,165 @@
+/*
+ * spsattn.h — C ABI of libspsattn.so: the SPS Transformer attention hot path
+ * (prefill attention over the doubled input/<predict> sequence, segmented decode
+ * attention over the persistent KV cache plus the predict ring, and the decode
+ * KV-cache update) as hand-written sm_100a CUDA.
+ *
+ * Conventions
+ *   - every pointer named "device" is a CUDA device pointer on the current device;
+ *     the library never allocates device memory (workspaces are caller-owned);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream); all work is
+ *     enqueued on it and the call returns without synchronising;
+ *   - return value: 0 ok; <0 argument error found on the host before any launch
+ *     (spsattn_strerror explains); >0 CUDA runtime / driver error code;
+ *   - kernels never trap: a bounded wait that expires writes a non-zero code into
+ *     the caller's `device_status` word (may be NULL) and the block returns.
+ *
+ * Reference interface each entry point stands in for (paths inside lil-lab/sps):
+ *   spsattn_prefill_fwd      src/modeling/models/attention/triton_sps_flash_attention.py:491-620 (wrapper)
+ *                            and :147-269 (_attn_fwd_sps); the reverse and standard variants
+ *                            triton_reverse_sps_flash_attention.py:242-331, triton_full_flash_attention.py:204-283
+ *   spsattn_decode_fwd       src/modeling/models/utils/decode_attention.py:483-594 (q=2), :393-480 (q=1)
+ *   spsattn_kv_update        src/modeling/models/utils/decode_attention_fast.py:139-221
+ */
+#ifndef SPSATTN_H_
+#define SPSATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPSATTN_DTYPE_BF16 0
+#define SPSATTN_DTYPE_FP16 1
+
+/* which key parity of the doubled sequence is persistent (window-exempt) */
+#define SPSATTN_PARITY_EVEN 0   /* SPS: input token slot            (triton_sps_flash_attention.py:97) */
+#define SPSATTN_PARITY_ODD 1    /* Reverse-SPS / Delayed-State      (triton_reverse_sps_flash_attention.py:123) */
+#define SPSATTN_PARITY_NONE (-1) /* Standard: causal + document mask (triton_full_flash_attention.py:95-104) */
+
+#define SPSATTN_NO_WINDOW (-2147483647 - 1) /* persistent_window: no persistent-key window */
+
+/* mask_flags */
+#define SPSATTN_FLAG_PERSISTENT_Q_SKIPS_TEMPORARY 1 /* rows of persistent parity see no temporary keys */
+
+/* error codes (<0) */
+#define SPSATTN_ERR_ARG (-1)        /* null pointer, bad enum, bad size */
+#define SPSATTN_ERR_HEAD_DIM (-2)   /* head_dim not supported by this entry point */
+#define SPSATTN_ERR_ALIGN (-3)      /* pointer or stride not 16-byte aligned */
+#define SPSATTN_ERR_WORKSPACE (-4)  /* workspace missing or too small */
+#define SPSATTN_ERR_ODD_LENGTH (-5) /* doubled sequence length must be even */
+#define SPSATTN_ERR_DRIVER (-6)     /* tensor-map encoder unavailable */
+#define SPSATTN_ERR_TOO_LARGE (-7)  /* size beyond a documented maximum */
+
+/* device_status codes written by kernels (0 = ok) */
+#define SPSATTN_STATUS_WAIT_EXPIRED 1
+
+const char* spsattn_strerror(int code);
+int spsattn_version(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Prefill: O = softmax(mask(Q K^T * sm_scale)) V over [B, H, N, D] row-major contiguous tensors.
+ *
+ * Visibility of key row j to query row i (tok = row / 2), the reference rule
+ * (triton_sps_flash_attention.py:81-111):
+ *     j <= i  AND  doc[b][i] == doc[b][j] (if doc_ids given)
+ *     AND ( j%2 == persistent_parity ? (persistent_window unset OR tok_i - tok_j <= persistent_window OR i == j)
+ *                                    : tok_i - tok_j <= temporary_window )
+ * With SPSATTN_PARITY_NONE only the causal and document terms apply.  Rows with no visible key
+ * produce 0.  doc_ids: [B, N] int64 (doc_is_i64 = 1) or int32, element strides given; NULL = none.
+ * lse (nullable, [B, H, N] fp32) receives log2(sum_j exp2(score_ij * sm_scale * log2 e)), the
+ * reference's M tensor (:265-267).  N must be even unless parity is NONE.  D in {64, 128} run on
+ * the tcgen05/TMA kernel; D in {16, 32, 256} run on a plain CUDA-core kernel.  sm_scale > 0.
+ * workspace: at least spsattn_prefill_workspace_bytes(B, H, N, D) bytes of device memory,
+ * 256-byte aligned, private to this call until it completes.
+ * ------------------------------------------------------------------------------------------- */
+size_t spsattn_prefill_workspace_bytes(int B, int H, int N, int D);
+
+int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                        const void* doc_ids, int doc_is_i64, int64_t doc_stride_b, int64_t doc_stride_t,
+                        int B, int H, int N, int D, int dtype, float sm_scale,
+                        int persistent_parity, int temporary_window, int persistent_window,
+                        int mask_flags,
+                        void* workspace, size_t workspace_bytes,
+                        int* device_status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Decode: nq (1 or 2) queries per (sequence, head) over up to 3 length-masked KV segments plus up
+ * to 2 single-token "current" K/V entries; fp32 output [S, nq, H, D].
+ *
+ * Segment table (the reference's KVSegment, decode_attention.py:21-32, generalised so a packed
+ * cache needs no copy): key row r of (sequence s, head h) lives at element offset
+ *     (seq_offset ? seq_offset[s] : s * seq_stride) + h * head_stride + r * row_stride
+ * from k / v, rows are D contiguous elements, and rows [0, min(len, max_rows)) are live, where
+ * len = lengths[s] (lengths_per_head = 0) or lengths[s * H + h] (= 1), int64 on the device.
+ * query_mask bit i set: query slot i scans this segment / sees this extra entry.  The reference's
+ * q=2 call is segments {ring, retained} with query_mask 3, extras {current normal: 3, current
+ * predict: 2} (decode_attention.py:309-361).  No visible key => output 0 (:363-366).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct spsattn_segment {
+  const void* k;              /* device */
+  const void* v;              /* device */
+  const int64_t* seq_offset;  /* device [S] element offsets, or NULL */
+  int64_t seq_stride;         /* elements, used when seq_offset is NULL */
+  int64_t head_stride;        /* elements */
+  int64_t row_stride;         /* elements, >= D */
+  const int64_t* lengths;     /* device [S] or [S*H] */
+  int32_t lengths_per_head;   /* 0 or 1 */
+  int32_t max_rows;           /* host cap on rows scanned: min(storage, max_len_cap) */
+  uint32_t query_mask;
+  uint32_t reserved;
+} spsattn_segment;
+
+typedef struct spsattn_extra {
+  const void* k; /* device [S, H, D] contiguous */
+  const void* v; /* device [S, H, D] contiguous */
+  uint32_t query_mask;
+  uint32_t reserved;
+} spsattn_extra;
+
+size_t spsattn_decode_workspace_bytes(int S, int H, int D, int nq, const spsattn_segment* segs,
+                                      int n_segments);
+
+/* q: device [S, nq, H, D] contiguous, dtype as given; out: device fp32 [S, nq, H, D].
+ * D multiple of 8, 8 <= D <= 256.  Split-K over each (sequence, head): partial (max, sum,
+ * accumulator) records go to `workspace`, then a merge pass writes `out`. */
+int spsattn_decode_fwd(const void* q, int nq, float* out,
+                       const spsattn_segment* segs, int n_segments,
+                       const spsattn_extra* extras, int n_extras,
+                       int S, int H, int D, int dtype, float sm_scale,
+                       void* workspace, size_t workspace_bytes,
+                       int* device_status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Decode KV-cache update, in place (decode_attention_fast.py:34-136): for every active sequence
+ * insert k_window/v_window into the ring [S,H,window_storage,D] at `pos` when the ring is full
+ * (len >= window_tokens) else at `len`, then pos = (pos+1) % window_tokens or len += 1; append
+ * k_retained/v_retained to the retained cache [S,H,retained_storage,D] at len[s,h] when in
+ * bounds and increment it.  window_tokens <= 0: retained part only (ring pointers may be NULL).
+ * nw_len, nw_pos: int64 [S]; br_len: int64 [S,H]; active: int8 [S]; new K/V [S,H,D] in the
+ * cache dtype (elem_bytes 2 or 4).
+ * ------------------------------------------------------------------------------------------- */
+int spsattn_kv_update(void* nw_k, void* nw_v, int64_t* nw_len, int64_t* nw_pos,
+                      void* br_k, void* br_v, int64_t* br_len,
+                      const void* k_window, const void* v_window,
+                      const void* k_retained, const void* v_retained,
+                      const int8_t* active,
+                      int S, int H, int D, int window_storage, int retained_storage,
+                      int window_tokens, int elem_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Test hook: the boolean visibility the prefill kernels apply, evaluated on the device with the
+ * same per-row key-interval arithmetic (and the same document pre-pass) the kernels use, written
+ * as bytes [B, N, N].  For bit-exact mask checks at small N (N <= 4096).
+ * ------------------------------------------------------------------------------------------- */
+int spsattn_debug_visibility(uint8_t* vis, const void* doc_ids, int doc_is_i64,
+                             int64_t doc_stride_b, int64_t doc_stride_t, int B, int N,
+                             int persistent_parity, int temporary_window, int persistent_window,
+                             int mask_flags, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPSATTN_H_ */

@@ -1,0 +1,21 @@
+"""sps_b200: the SPS Transformer attention hot path as hand-written sm_100a CUDA.
+
+The package is a thin host layer over ``libspsattn.so`` (C ABI in ``include/spsattn.h``):
+prefill attention (``attention``), segmented decode attention and the decode KV-cache
+update (``decode``), and ``install()`` which rebinds the reference model classes to them.
+"""
+
+from . import _lib
+from .attention import (check_device_status, full_attention, prefill_attention,
+                        reverse_sps_sliding_attention, sps_sliding_attention)
+from .decode import (KVSegment, PackedKVSegment, decode_attention, fused_sps_kv_update,
+                     masked_kv_attention, segmented_q1_attention, segmented_q2_attention,
+                     triton_segmented_q2_attention)
+from .install import install
+
+__all__ = [
+    "KVSegment", "PackedKVSegment", "check_device_status", "decode_attention", "full_attention",
+    "fused_sps_kv_update", "install", "masked_kv_attention", "prefill_attention",
+    "reverse_sps_sliding_attention", "segmented_q1_attention", "segmented_q2_attention",
+    "sps_sliding_attention", "triton_segmented_q2_attention",
+]

@@ -1,0 +1,86 @@
+"""ctypes binding of libspsattn.so (the C ABI declared in include/spsattn.h).
+
+There is no fallback: if the shared library is missing or fails to load, every
+entry point raises.  Build it with ``python -m sps_b200.build``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libspsattn.so")
+
+DTYPE_BF16, DTYPE_FP16 = 0, 1
+PARITY_EVEN, PARITY_ODD, PARITY_NONE = 0, 1, -1
+NO_WINDOW = -2147483648
+FLAG_PERSISTENT_Q_SKIPS_TEMPORARY = 1
+
+EXPORTS = (
+    "spsattn_version", "spsattn_strerror",
+    "spsattn_prefill_workspace_bytes", "spsattn_prefill_fwd",
+    "spsattn_decode_workspace_bytes", "spsattn_decode_fwd",
+    "spsattn_kv_update", "spsattn_debug_visibility",
+)
+
+
+class Segment(C.Structure):
+    """struct spsattn_segment"""
+    _fields_ = [
+        ("k", C.c_void_p), ("v", C.c_void_p), ("seq_offset", C.c_void_p),
+        ("seq_stride", C.c_int64), ("head_stride", C.c_int64), ("row_stride", C.c_int64),
+        ("lengths", C.c_void_p), ("lengths_per_head", C.c_int32), ("max_rows", C.c_int32),
+        ("query_mask", C.c_uint32), ("reserved", C.c_uint32),
+    ]
+
+
+class Extra(C.Structure):
+    """struct spsattn_extra"""
+    _fields_ = [("k", C.c_void_p), ("v", C.c_void_p), ("query_mask", C.c_uint32),
+                ("reserved", C.c_uint32)]
+
+
+class SpsAttnError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library once and declare the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise SpsAttnError(
+            f"{LIB_PATH} is missing: the CUDA extension is required (python -m sps_b200.build); "
+            "there is no CPU or PyTorch fallback")
+    lib = C.CDLL(LIB_PATH)
+    vp, i32, i64, f32, sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+    lib.spsattn_version.restype = i32
+    lib.spsattn_strerror.restype = C.c_char_p
+    lib.spsattn_strerror.argtypes = [i32]
+    lib.spsattn_prefill_workspace_bytes.restype = sz
+    lib.spsattn_prefill_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    lib.spsattn_prefill_fwd.restype = i32
+    lib.spsattn_prefill_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i64, i32, i32, i32, i32, i32,
+                                        f32, i32, i32, i32, i32, vp, sz, vp, vp]
+    lib.spsattn_decode_workspace_bytes.restype = sz
+    lib.spsattn_decode_workspace_bytes.argtypes = [i32, i32, i32, i32, C.POINTER(Segment), i32]
+    lib.spsattn_decode_fwd.restype = i32
+    lib.spsattn_decode_fwd.argtypes = [vp, i32, vp, C.POINTER(Segment), i32, C.POINTER(Extra), i32,
+                                       i32, i32, i32, i32, f32, vp, sz, vp, vp]
+    lib.spsattn_kv_update.restype = i32
+    lib.spsattn_kv_update.argtypes = [vp] * 12 + [i32] * 7 + [vp]
+    lib.spsattn_debug_visibility.restype = i32
+    lib.spsattn_debug_visibility.argtypes = [vp, vp, i32, i64, i64, i32, i32, i32, i32, i32, i32, vp, sz, vp]
+    _lib = lib
+    return lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = load().spsattn_strerror(code).decode()
+        raise SpsAttnError(f"{what} failed: {msg} (code {code})")

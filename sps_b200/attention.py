@@ -1,0 +1,166 @@
+"""Prefill attention of the SPS model family on sm_100a, behind the reference's call signatures.
+
+``sps_sliding_attention``, ``reverse_sps_sliding_attention`` and ``full_attention`` take the
+same arguments, in the same order and with the same meaning, as the reference's
+src/modeling/models/attention/triton_sps_flash_attention.py:725-753,
+triton_reverse_sps_flash_attention.py:827-853 and triton_full_flash_attention.py:679-709, so the
+model classes can call them unchanged (see ``sps_b200.install``).  They are forward only.
+All compute happens in libspsattn.so (tcgen05 / TMA kernel for head_dim 64 and 128).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_SUPPORTED_HEAD_DIMS = (16, 32, 64, 128, 256)   # triton_sps_flash_attention.py:510
+_status_words: dict = {}
+
+
+def _status(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when a bounded wait expires."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if any kernel reported a failure (a bounded wait that expired)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status(dev)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise _lib.SpsAttnError(f"device reported status {code} (a bounded wait expired)")
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.DTYPE_BF16
+    if t.dtype == torch.float16:
+        return _lib.DTYPE_FP16
+    raise TypeError(f"sps_b200 attention computes in bf16 or fp16, got {t.dtype}")
+
+
+def _forward_only(*tensors) -> None:
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        raise RuntimeError(
+            "sps_b200 attention is forward only: call it under torch.no_grad() / inference_mode(), "
+            "or detach the inputs (the backward kernels are not part of this library)")
+
+
+def prefill_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    sm_scale: float,
+    *,
+    persistent_parity: int,
+    temporary_window: int = 0,
+    persistent_window: Optional[int] = None,
+    documents_idx: Optional[torch.Tensor] = None,
+    mask_flags: int = 0,
+    return_lse: bool = False,
+    out: Optional[torch.Tensor] = None,
+):
+    """Masked attention over [B, H, N, D] tensors; the general entry the three wrappers share.
+
+    ``persistent_parity``: 0 (SPS), 1 (Reverse-SPS / Delayed-State) or -1 (Standard).
+    Returns O (same dtype as q) and, with ``return_lse``, the base-2 log-sum-exp [B, H, N] fp32.
+    """
+    lib = _lib.load()
+    if not q.is_cuda:
+        raise RuntimeError("sps_b200 attention needs CUDA tensors; there is no CPU path")
+    _forward_only(q, k, v)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, H, N, D = q.shape
+    assert k.shape == q.shape and v.shape == q.shape, "q, k, v must have the same shape"
+    assert k.dtype == q.dtype and v.dtype == q.dtype, "q, k, v must have the same dtype"
+    assert D in _SUPPORTED_HEAD_DIMS, f"head_dim must be one of {_SUPPORTED_HEAD_DIMS}"
+    if persistent_parity != _lib.PARITY_NONE:
+        assert N % 2 == 0, "Expected doubled sequence length (2T)."
+    dt = _dtype_code(q)
+    docs_ptr, docs_i64, sb, st = None, 0, 0, 0
+    if documents_idx is not None:
+        docs = documents_idx
+        assert docs.shape[0] == B and docs.shape[1] == N
+        assert docs.is_cuda and docs.device == q.device
+        if docs.dtype not in (torch.int64, torch.int32):
+            docs = docs.to(torch.int64)
+        docs_ptr, docs_i64 = docs.data_ptr(), int(docs.dtype == torch.int64)
+        sb, st = docs.stride()
+    o = torch.empty_like(q) if out is None else out
+    lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device) if return_lse else None
+    ws_bytes = lib.spsattn_prefill_workspace_bytes(B, H, N, D) if documents_idx is not None else 0
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
+    pw = _lib.NO_WINDOW if persistent_window is None else max(-1, min(int(persistent_window), N))
+    with torch.cuda.device(q.device):
+        rc = lib.spsattn_prefill_fwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+            None if lse is None else lse.data_ptr(),
+            docs_ptr, docs_i64, sb, st, B, H, N, D, dt, float(sm_scale), int(persistent_parity),
+            max(-1, min(int(temporary_window), N)), pw, int(mask_flags),
+            None if ws is None else ws.data_ptr(), ws_bytes,
+            _status(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "spsattn_prefill_fwd")
+    return (o, lse) if return_lse else o
+
+
+def sps_sliding_attention(q, k, v, sm_scale, temporary_key_window, warp_specialize=True,
+                          documents_idx_BxT=None, persistent_key_window=None):
+    """SPS variant: the persistent (window-exempt) key is the even / input slot, the <predict>
+    slot is windowed.  ``warp_specialize`` is accepted for signature compatibility and ignored.
+    """
+    del warp_specialize
+    return prefill_attention(q, k, v, sm_scale, persistent_parity=_lib.PARITY_EVEN,
+                             temporary_window=int(temporary_key_window),
+                             persistent_window=persistent_key_window,
+                             documents_idx=documents_idx_BxT)
+
+
+def reverse_sps_sliding_attention(q, k, v, sm_scale, temporary_key_window, warp_specialize=True,
+                                  documents_idx_BxT=None, persistent_key_window=None):
+    """Reverse-SPS / Delayed-State variant: the persistent key is the odd slot."""
+    del warp_specialize
+    return prefill_attention(q, k, v, sm_scale, persistent_parity=_lib.PARITY_ODD,
+                             temporary_window=int(temporary_key_window),
+                             persistent_window=persistent_key_window,
+                             documents_idx=documents_idx_BxT)
+
+
+def full_attention(q, k, v, sm_scale, warp_specialize=True, documents_idx_BxT=None):
+    """Standard model: causal attention with an optional same-document mask."""
+    del warp_specialize
+    return prefill_attention(q, k, v, sm_scale, persistent_parity=_lib.PARITY_NONE,
+                             documents_idx=documents_idx_BxT)
+
+
+def visibility(n_ctx: int, *, persistent_parity: int, temporary_window: int = 0,
+               persistent_window: Optional[int] = None, documents_idx: Optional[torch.Tensor] = None,
+               mask_flags: int = 0, batch: int = 1, device="cuda") -> torch.Tensor:
+    """The boolean mask the kernels apply, evaluated on the device ([B, N, N] bool); test hook."""
+    lib = _lib.load()
+    dev = torch.device(device)
+    B = batch if documents_idx is None else documents_idx.shape[0]
+    vis = torch.empty((B, n_ctx, n_ctx), dtype=torch.uint8, device=dev)
+    docs_ptr, docs_i64, sb, st, ws, ws_bytes = None, 0, 0, 0, None, 0
+    if documents_idx is not None:
+        docs = documents_idx.to(dev)
+        if docs.dtype not in (torch.int64, torch.int32):
+            docs = docs.to(torch.int64)
+        docs_ptr, docs_i64 = docs.data_ptr(), int(docs.dtype == torch.int64)
+        sb, st = docs.stride()
+        ws_bytes = lib.spsattn_prefill_workspace_bytes(B, 1, n_ctx, 64)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    pw = _lib.NO_WINDOW if persistent_window is None else max(-1, min(int(persistent_window), n_ctx))
+    with torch.cuda.device(dev):
+        rc = lib.spsattn_debug_visibility(
+            vis.data_ptr(), docs_ptr, docs_i64, sb, st, B, n_ctx, int(persistent_parity),
+            max(-1, min(int(temporary_window), n_ctx)), pw, int(mask_flags),
+            None if ws is None else ws.data_ptr(), ws_bytes, torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "spsattn_debug_visibility")
+    return vis.bool()

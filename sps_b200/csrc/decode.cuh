@@ -1,0 +1,271 @@
+// Segmented decode attention: nq (1 or 2) queries per (sequence, head) over up to three
+// length-masked KV segments plus up to two single-token "current" entries.
+//
+// The job is bandwidth bound (every live K/V row is read exactly once, both queries share the
+// load), so it is split-K: the live rows of one (sequence, head) — the segments laid end to
+// end — are cut into chunks of `chunk_rows`, one block per chunk.  A block streams its rows with
+// 128-bit loads (D/8 lanes per row, four row batches in flight per lane), keeps an online
+// softmax per lane group in fp32, merges the groups and writes one (max, sum, acc[D]) record
+// per query into the workspace; a second small kernel merges the records of each
+// (sequence, head) and writes fp32 output.  Lengths are read on the device, so the grid is
+// sized from the host-side caps and blocks past the live length return at once.
+// Reference computation: src/modeling/models/utils/decode_attention.py:191-368.
+#pragma once
+
+#include "common.cuh"
+
+namespace spsattn {
+
+constexpr int kMaxSegments = 3;
+constexpr int kMaxExtras = 2;
+constexpr int kDecodeThreads = 128;
+constexpr int kDecodeUnroll = 4;
+
+struct DecodeSeg {
+  const void* k;
+  const void* v;
+  const int64_t* seq_offset;
+  int64_t seq_stride, head_stride, row_stride;
+  const int64_t* lengths;
+  int lengths_per_head;
+  int max_rows;
+  uint32_t query_mask;
+};
+
+struct DecodeParams {
+  const void* q;       // [S, nq, H, D]
+  float* out;          // [S, nq, H, D]
+  float* partial;      // [S*H][n_chunks][nq][D + 2]
+  DecodeSeg seg[kMaxSegments];
+  const void* extra_k[kMaxExtras];
+  const void* extra_v[kMaxExtras];
+  uint32_t extra_mask[kMaxExtras];
+  int n_segments, n_extras;
+  int S, H, nq;
+  int chunk_rows, n_chunks;
+  float scale_log2;
+};
+
+__device__ __forceinline__ int live_rows(const DecodeSeg& sg, int s, int h, int H) {
+  long long len = sg.lengths_per_head ? sg.lengths[(size_t)s * H + h] : sg.lengths[s];
+  if (len < 0) len = 0;
+  return len < sg.max_rows ? (int)len : sg.max_rows;
+}
+
+template <int D, int NQ, bool FP16>
+__global__ void __launch_bounds__(kDecodeThreads)
+decode_split_kernel(const DecodeParams prm) {
+  constexpr int LPR = D / 8;          // lanes per row
+  constexpr int RPI = 32 / LPR;       // rows per warp load instruction
+  constexpr int U = kDecodeUnroll;
+  constexpr int STEP = 4 * RPI * U;   // rows per block step
+  static_assert(D % 8 == 0 && 32 % LPR == 0, "head_dim");
+
+  const int sh = blockIdx.x;
+  const int s = sh / prm.H, h = sh % prm.H;
+  const int chunk = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane / LPR;           // row inside a load instruction
+  const int dl = (lane % LPR) * 8;    // first of this lane's 8 dims
+
+  int seg_start[kMaxSegments + 1];
+  seg_start[0] = 0;
+#pragma unroll
+  for (int x = 0; x < kMaxSegments; ++x)
+    seg_start[x + 1] = seg_start[x] + (x < prm.n_segments ? live_rows(prm.seg[x], s, h, prm.H) : 0);
+  const int n_total = seg_start[kMaxSegments];
+  const int c_lo = chunk * prm.chunk_rows;
+  if (chunk > 0 && c_lo >= n_total) return;
+  const int c_hi = min(c_lo + prm.chunk_rows, n_total);
+
+  // queries, pre-scaled so scores are in the log2 domain
+  float q[NQ][8];
+#pragma unroll
+  for (int qi = 0; qi < NQ; ++qi) {
+    const uint4 u = *reinterpret_cast<const uint4*>(
+        reinterpret_cast<const uint16_t*>(prm.q) + (((size_t)s * NQ + qi) * prm.H + h) * D + dl);
+    unpack2<FP16>(u.x, q[qi][0], q[qi][1]);
+    unpack2<FP16>(u.y, q[qi][2], q[qi][3]);
+    unpack2<FP16>(u.z, q[qi][4], q[qi][5]);
+    unpack2<FP16>(u.w, q[qi][6], q[qi][7]);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) q[qi][x] *= prm.scale_log2;
+  }
+
+  float m_run[NQ], l_run[NQ], acc[NQ][8];
+#pragma unroll
+  for (int qi = 0; qi < NQ; ++qi) {
+    m_run[qi] = -1.0e30f;
+    l_run[qi] = 0.f;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) acc[qi][x] = 0.f;
+  }
+
+  // one batch of U rows (one per unroll slot) for this lane group
+  auto process = [&](const uint16_t* kb, const uint16_t* vb, int64_t row_stride, int r0, int r_hi,
+                     uint32_t qmask) {
+    uint4 kr[U], vr[U];
+    bool valid[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int r = r0 + u * (4 * RPI);
+      valid[u] = r < r_hi;
+      if (valid[u]) {
+        kr[u] = __ldg(reinterpret_cast<const uint4*>(kb + (size_t)r * row_stride + dl));
+        vr[u] = __ldg(reinterpret_cast<const uint4*>(vb + (size_t)r * row_stride + dl));
+      } else {
+        kr[u] = make_uint4(0, 0, 0, 0);
+        vr[u] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    float sc[NQ][U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float kf[8];
+      unpack2<FP16>(kr[u].x, kf[0], kf[1]);
+      unpack2<FP16>(kr[u].y, kf[2], kf[3]);
+      unpack2<FP16>(kr[u].z, kf[4], kf[5]);
+      unpack2<FP16>(kr[u].w, kf[6], kf[7]);
+#pragma unroll
+      for (int qi = 0; qi < NQ; ++qi) {
+        float d = 0.f;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) d = fmaf(q[qi][x], kf[x], d);
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        sc[qi][u] = (valid[u] && ((qmask >> qi) & 1u)) ? d : -INFINITY;
+      }
+    }
+    float pr[NQ][U], alpha[NQ];
+#pragma unroll
+    for (int qi = 0; qi < NQ; ++qi) {
+      float mx = m_run[qi];
+#pragma unroll
+      for (int u = 0; u < U; ++u) mx = fmaxf(mx, sc[qi][u]);
+      alpha[qi] = fast_exp2(m_run[qi] - mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        pr[qi][u] = fast_exp2(sc[qi][u] - mx);
+        sum += pr[qi][u];
+      }
+      l_run[qi] = l_run[qi] * alpha[qi] + sum;
+      m_run[qi] = mx;
+#pragma unroll
+      for (int x = 0; x < 8; ++x) acc[qi][x] *= alpha[qi];
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float vf[8];
+      unpack2<FP16>(vr[u].x, vf[0], vf[1]);
+      unpack2<FP16>(vr[u].y, vf[2], vf[3]);
+      unpack2<FP16>(vr[u].z, vf[4], vf[5]);
+      unpack2<FP16>(vr[u].w, vf[6], vf[7]);
+#pragma unroll
+      for (int qi = 0; qi < NQ; ++qi)
+#pragma unroll
+        for (int x = 0; x < 8; ++x) acc[qi][x] = fmaf(pr[qi][u], vf[x], acc[qi][x]);
+    }
+  };
+
+#pragma unroll
+  for (int x = 0; x < kMaxSegments; ++x) {
+    if (x >= prm.n_segments) break;
+    const int lo = max(c_lo, seg_start[x]) - seg_start[x];
+    const int hi = min(c_hi, seg_start[x + 1]) - seg_start[x];
+    if (lo >= hi) continue;
+    const DecodeSeg& sg = prm.seg[x];
+    const int64_t base = (sg.seq_offset ? sg.seq_offset[s] : (int64_t)s * sg.seq_stride) +
+                         (int64_t)h * sg.head_stride;
+    const uint16_t* kb = reinterpret_cast<const uint16_t*>(sg.k) + base;
+    const uint16_t* vb = reinterpret_cast<const uint16_t*>(sg.v) + base;
+    for (int r = lo + warp * RPI + g; r - (warp * RPI + g) < hi; r += STEP)
+      process(kb, vb, sg.row_stride, r, hi, sg.query_mask);
+  }
+  if (chunk == 0 && warp == 0) {
+    // the current-token entries: one row each, handled by lane group 0 of warp 0
+    for (int e = 0; e < prm.n_extras; ++e) {
+      const uint16_t* kb = reinterpret_cast<const uint16_t*>(prm.extra_k[e]) + (size_t)sh * D;
+      const uint16_t* vb = reinterpret_cast<const uint16_t*>(prm.extra_v[e]) + (size_t)sh * D;
+      process(kb, vb, 0, g, 1, prm.extra_mask[e]);
+    }
+  }
+
+  // merge the lane groups of a warp, then the four warps, then write the record
+#pragma unroll
+  for (int qi = 0; qi < NQ; ++qi) {
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m_run[qi], o);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l_run[qi], o);
+      const float mx = fmaxf(m_run[qi], m_o);
+      const float a = fast_exp2(m_run[qi] - mx), bsc = fast_exp2(m_o - mx);
+      l_run[qi] = l_run[qi] * a + l_o * bsc;
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        const float acc_o = __shfl_xor_sync(0xffffffffu, acc[qi][x], o);
+        acc[qi][x] = acc[qi][x] * a + acc_o * bsc;
+      }
+      m_run[qi] = mx;
+    }
+  }
+  __shared__ float s_m[4][NQ], s_l[4][NQ], s_acc[4][NQ][D];
+  if (g == 0) {
+#pragma unroll
+    for (int qi = 0; qi < NQ; ++qi) {
+      if (lane == 0) {
+        s_m[warp][qi] = m_run[qi];
+        s_l[warp][qi] = l_run[qi];
+      }
+#pragma unroll
+      for (int x = 0; x < 8; ++x) s_acc[warp][qi][dl + x] = acc[qi][x];
+    }
+  }
+  __syncthreads();
+  float* rec = prm.partial + ((size_t)sh * prm.n_chunks + chunk) * NQ * (D + 2);
+  for (int idx = tid; idx < NQ * D; idx += kDecodeThreads) {
+    const int qi = idx / D, d = idx % D;
+    float mx = s_m[0][qi];
+#pragma unroll
+    for (int w = 1; w < 4; ++w) mx = fmaxf(mx, s_m[w][qi]);
+    float a = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = fast_exp2(s_m[w][qi] - mx);
+      a += s_acc[w][qi][d] * f;
+      l += s_l[w][qi] * f;
+    }
+    rec[qi * (D + 2) + 2 + d] = a;
+    if (d == 0) {
+      rec[qi * (D + 2)] = mx;
+      rec[qi * (D + 2) + 1] = l;
+    }
+  }
+}
+
+// One block of D threads per (sequence, head, query): merge the chunk records.
+template <int D, int NQ>
+__global__ void __launch_bounds__(D)
+decode_merge_kernel(const DecodeParams prm) {
+  const int sh = blockIdx.x;
+  const int qi = blockIdx.y;
+  const int s = sh / prm.H, h = sh % prm.H;
+  const int d = threadIdx.x;
+  int n_total = 0;
+  for (int x = 0; x < prm.n_segments; ++x) n_total += live_rows(prm.seg[x], s, h, prm.H);
+  int n_chunks = (n_total + prm.chunk_rows - 1) / prm.chunk_rows;
+  if (n_chunks < 1) n_chunks = 1;
+  const float* rec0 = prm.partial + (size_t)sh * prm.n_chunks * NQ * (D + 2) + qi * (D + 2);
+  float mx = -1.0e30f;
+  for (int c = 0; c < n_chunks; ++c) mx = fmaxf(mx, rec0[(size_t)c * NQ * (D + 2)]);
+  float a = 0.f, l = 0.f;
+  for (int c = 0; c < n_chunks; ++c) {
+    const float* rec = rec0 + (size_t)c * NQ * (D + 2);
+    const float f = fast_exp2(rec[0] - mx);
+    l += rec[1] * f;
+    a += rec[2 + d] * f;
+  }
+  prm.out[(((size_t)s * NQ + qi) * prm.H + h) * D + d] = l > 0.f ? a / l : 0.f;
+}
+
+}  // namespace spsattn

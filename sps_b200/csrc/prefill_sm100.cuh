@@ -1,0 +1,452 @@
+// SPS prefill attention for sm_100a: TMA-staged Q/K/V tiles, tcgen05 MMAs accumulating in TMEM,
+// online softmax in registers (one query row per thread, no shuffles), key streams
+// de-interleaved by parity so that only tiles that hold visible keys are visited.
+//
+// One block = one 128-row query tile of one (batch, head).  Roles:
+//   warps 0-3  softmax / correction / epilogue (thread r owns query row r = TMEM lane r)
+//   warp 4     TMEM allocation, TMA producer (lane 0)
+//   warp 5     MMA issuer (lane 0)
+// Per key tile j (128 key tokens of one parity stream):
+//   S = Q K_j^T        tcgen05.mma  128x128xD, operands K-major / 128B swizzle in shared memory
+//   P = exp2(S*c - m*c) softmax warps: tcgen05.ld S -> registers, mask boundary tiles only,
+//                       bf16/fp16 P written to shared memory in the K-major swizzled layout
+//   O += P V_j         tcgen05.mma  128xDx128, V consumed as the MN-major B operand as loaded
+// Reference computation: src/modeling/models/attention/triton_sps_flash_attention.py:26-139,
+// :147-269 (and the reverse / standard variants); unlike it, tiles whose keys are all hidden
+// by the document / window / parity rule are never loaded or multiplied.
+#pragma once
+
+#include "common.cuh"
+#include "mask.cuh"
+
+namespace spsattn {
+
+struct PrefillParams {
+  void* o;               // [B,H,N,D]
+  float* lse;            // [B,H,N] or null
+  const void* docs;      // [B,N] ids or null
+  int64_t doc_stride_b, doc_stride_t;
+  int doc_is_i64;
+  const int* lo;         // [B,N] run starts (pre-pass) or null
+  const int* mono;       // [B] 1 when ids of the row are non-decreasing, or null
+  int B, H, N;
+  int n_qtiles;
+  MaskParams mask;
+  float scale_log2;      // sm_scale * log2(e)
+  int* status;
+};
+
+constexpr int kTileM = 128;      // query rows per block
+constexpr int kTileN = 128;      // key tokens per tile
+constexpr int kPrefillThreads = 192;
+
+template <int D>
+struct PrefillCfg {
+  static constexpr int kStagesK = 2;
+  static constexpr int kStagesV = (D == 64) ? 1 : 2;
+  static constexpr int kSBufs = (D == 64) ? 1 : 2;           // S accumulators in TMEM
+  static constexpr uint32_t kTmemCols = (D == 64) ? 256 : 512;
+  static constexpr uint32_t kColO = kSBufs * 128;             // O accumulator column offset
+  static constexpr int kTileBytes = kTileN * D * 2;           // one Q / K / V tile
+  static constexpr int kSubTileBytes = kTileN * 128;          // 128 rows x 64 elements
+  static constexpr int kPBytes = kTileM * kTileN * 2;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffK = kOffQ + kTileBytes;
+  static constexpr int kOffV = kOffK + kStagesK * kTileBytes;
+  static constexpr int kOffP = kOffV + kStagesV * kTileBytes;
+  static constexpr int kOffBar = kOffP + kPBytes;
+  static constexpr int kSmemBytes = kOffBar + 256 + 1024;     // barriers + alignment slack
+  static constexpr int kBlocksPerSM = (D == 64) ? 2 : 1;
+};
+
+struct TileInfo {
+  int stream;   // key parity (0 in standard mode)
+  int k0;       // first key token of the tile (may be negative: zero-filled, masked)
+  int masked;   // element mask needed
+};
+
+struct BlockPlan {
+  StreamPlan sp[2];
+  int stream_id[2];
+  int n_streams;
+  int n_tiles;
+  int general_docs;  // ids are not monotone: compare ids element by element
+};
+
+__device__ __forceinline__ TileInfo tile_info(const BlockPlan& bp, int j) {
+  TileInfo t;
+  int s = 0;
+  if (j >= bp.sp[0].ntiles) {
+    j -= bp.sp[0].ntiles;
+    s = 1;
+  }
+  t.stream = bp.stream_id[s];
+  t.k0 = bp.sp[s].top - (kTileN - 1) - kTileN * j;
+  t.masked = bp.sp[s].force_mask || bp.general_docs ||
+             !(bp.sp[s].kmin_hi <= t.k0 && bp.sp[s].kmax_lo >= t.k0 + kTileN - 1);
+  return t;
+}
+
+template <int D, bool FP16>
+__global__ void __launch_bounds__(kPrefillThreads, PrefillCfg<D>::kBlocksPerSM)
+prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const PrefillParams prm) {
+  using Cfg = PrefillCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ BlockPlan s_plan;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // heavy query tiles (late rows) first, all tiles of one (b,h) adjacent so K/V stay in L2
+  const int bh = blockIdx.x / prm.n_qtiles;
+  const int qt = prm.n_qtiles - 1 - (blockIdx.x % prm.n_qtiles);
+  const int b = bh / prm.H;
+  const int i0 = qt * kTileM;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = smem_base + Cfg::kOffQ;
+  const uint32_t sK = smem_base + Cfg::kOffK;
+  const uint32_t sV = smem_base + Cfg::kOffV;
+  const uint32_t sP = smem_base + Cfg::kOffP;
+  const uint32_t bar0 = smem_base + Cfg::kOffBar;
+  // barrier slots (8 bytes each)
+  const uint32_t bar_q_full = bar0;
+  const uint32_t bar_k_full = bar0 + 8;     // [2]
+  const uint32_t bar_k_empty = bar0 + 24;   // [2]
+  const uint32_t bar_v_full = bar0 + 40;    // [2]
+  const uint32_t bar_v_empty = bar0 + 56;   // [2]
+  const uint32_t bar_s_full = bar0 + 72;    // [2]
+  const uint32_t bar_s_free = bar0 + 88;    // [2]
+  const uint32_t bar_p_full = bar0 + 104;
+  const uint32_t bar_pv_done = bar0 + 112;
+
+  const bool has_docs = prm.docs != nullptr;
+
+  if (tid == 0) {
+    // a failure reported by an earlier block turns every later block into a no-op
+    s_abort = (prm.status != nullptr && *reinterpret_cast<volatile int*>(prm.status) != 0) ? 1 : 0;
+    BlockPlan bp;
+    bp.general_docs = (has_docs && prm.mono != nullptr && prm.mono[b] == 0) ? 1 : 0;
+    int lo0 = 0, lo1 = 0;
+    if (has_docs && !bp.general_docs) {
+      const int i1 = min(i0 + kTileM - 1, prm.N - 1);
+      lo0 = prm.lo[(size_t)b * prm.N + i0];
+      lo1 = prm.lo[(size_t)b * prm.N + i1];
+    }
+    if (prm.mask.ks == 1) {
+      bp.n_streams = 1;
+      bp.stream_id[0] = 0;
+      bp.stream_id[1] = 0;
+      bp.sp[0] = plan_stream(prm.mask, i0, lo0, lo1, 0, kTileN);
+      bp.sp[1] = bp.sp[0];
+      bp.sp[1].ntiles = 0;
+    } else {
+      bp.n_streams = 2;
+      bp.stream_id[0] = prm.mask.pp;       // persistent stream first: holds the diagonal
+      bp.stream_id[1] = 1 - prm.mask.pp;
+      bp.sp[0] = plan_stream(prm.mask, i0, lo0, lo1, bp.stream_id[0], kTileN);
+      bp.sp[1] = plan_stream(prm.mask, i0, lo0, lo1, bp.stream_id[1], kTileN);
+    }
+    bp.n_tiles = bp.sp[0].ntiles + bp.sp[1].ntiles;
+    s_plan = bp;
+
+    mbar_init(bar_q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_k_full + 8 * s, 1);
+      mbar_init(bar_k_empty + 8 * s, 1);
+      mbar_init(bar_v_full + 8 * s, 1);
+      mbar_init(bar_v_empty + 8 * s, 1);
+      mbar_init(bar_s_full + 8 * s, 1);
+      mbar_init(bar_s_free + 8 * s, 128);
+    }
+    mbar_init(bar_p_full, 128);
+    mbar_init(bar_pv_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 4) {
+    tmem_alloc<Cfg::kTmemCols>(smem_u32(&s_tmem_base));
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const uint32_t tmem = s_tmem_base;
+  const int n_tiles = s_plan.n_tiles;
+  volatile int* abort_flag = &s_abort;
+  const bool bail = s_abort != 0;
+
+  if (!bail && n_tiles > 0) {
+    if (warp == 4) {
+      // ------------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        mbar_arrive_expect_tx(bar_q_full, Cfg::kTileBytes);
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(sQ + c * Cfg::kSubTileBytes, &tm_q, bar_q_full, c * 64, i0, bh);
+        auto load_k = [&](int j) {
+          const TileInfo t = tile_info(s_plan, j);
+          const int st = j % Cfg::kStagesK;
+          if (j >= Cfg::kStagesK) {
+            if (!mbar_wait(bar_k_empty + 8 * st, ((j / Cfg::kStagesK) - 1) & 1, abort_flag, prm.status))
+              return false;
+          }
+          mbar_arrive_expect_tx(bar_k_full + 8 * st, Cfg::kTileBytes);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(sK + st * Cfg::kTileBytes + c * Cfg::kSubTileBytes, &tm_k, bar_k_full + 8 * st,
+                        c * 64, t.stream, t.k0, bh);
+          return true;
+        };
+        auto load_v = [&](int j) {
+          const TileInfo t = tile_info(s_plan, j);
+          const int st = j % Cfg::kStagesV;
+          if (j >= Cfg::kStagesV) {
+            if (!mbar_wait(bar_v_empty + 8 * st, ((j / Cfg::kStagesV) - 1) & 1, abort_flag, prm.status))
+              return false;
+          }
+          mbar_arrive_expect_tx(bar_v_full + 8 * st, Cfg::kTileBytes);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(sV + st * Cfg::kTileBytes + c * Cfg::kSubTileBytes, &tm_v, bar_v_full + 8 * st,
+                        c * 64, t.stream, t.k0, bh);
+          return true;
+        };
+        bool ok = load_k(0);
+        for (int j = 0; ok && j < n_tiles; ++j) {
+          if (j + 1 < n_tiles) ok = load_k(j + 1);
+          if (ok) ok = load_v(j);
+        }
+      }
+      __syncwarp();
+    } else if (warp == 5) {
+      // ------------------------------------------------------------------ MMA issuer
+      if (lane == 0) {
+        constexpr uint32_t idesc_qk = make_idesc_f16(FP16, kTileM, kTileN, false, false);
+        constexpr uint32_t idesc_pv = make_idesc_f16(FP16, kTileM, D, false, true);
+        auto issue_qk = [&](int j) {
+          const int st = j % Cfg::kStagesK;
+          const int sb = j % Cfg::kSBufs;
+          if (!mbar_wait(bar_k_full + 8 * st, (j / Cfg::kStagesK) & 1, abort_flag, prm.status)) return false;
+          if (j >= Cfg::kSBufs) {
+            if (!mbar_wait(bar_s_free + 8 * sb, ((j / Cfg::kSBufs) - 1) & 1, abort_flag, prm.status))
+              return false;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk / 4) * Cfg::kSubTileBytes + (kk % 4) * 32;
+            const uint64_t da = make_smem_desc_sw128(sQ + off, 16, 1024);
+            const uint64_t db = make_smem_desc_sw128(sK + st * Cfg::kTileBytes + off, 16, 1024);
+            umma_ss(tmem + sb * 128, da, db, idesc_qk, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(bar_s_full + 8 * sb);
+          umma_commit(bar_k_empty + 8 * st);
+          return true;
+        };
+        bool ok = mbar_wait(bar_q_full, 0, abort_flag, prm.status);
+        if (ok) ok = issue_qk(0);
+        for (int j = 0; ok && j < n_tiles; ++j) {
+          if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+          if (!ok) break;
+          const int st = j % Cfg::kStagesV;
+          if (!mbar_wait(bar_p_full, j & 1, abort_flag, prm.status)) break;
+          if (!mbar_wait(bar_v_full + 8 * st, (j / Cfg::kStagesV) & 1, abort_flag, prm.status)) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < kTileN / 16; ++kk) {
+            // P: K-major, two 64-key sub-tiles; V: MN-major, 16 key rows = 2048 bytes per step
+            const uint64_t da =
+                make_smem_desc_sw128(sP + (kk / 4) * (kTileM * 128) + (kk % 4) * 32, 16, 1024);
+            const uint64_t db = make_smem_desc_sw128(sV + st * Cfg::kTileBytes + kk * 2048,
+                                                     Cfg::kSubTileBytes, 1024);
+            umma_ss(tmem + Cfg::kColO, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_pv_done);
+          umma_commit(bar_v_empty + 8 * st);
+        }
+      }
+      __syncwarp();
+    } else {
+      // ------------------------------------------------------------------ softmax warps
+      const int row = tid;                 // TMEM lane and query row inside the tile
+      const int i = i0 + row;
+      const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+      const bool general = s_plan.general_docs != 0;
+      int lo_i = 0;
+      if (has_docs && !general && i < prm.N) lo_i = prm.lo[(size_t)b * prm.N + i];
+      int kmin_s[2], kmax_s[2];
+      row_interval(prm.mask, i, lo_i, 0, kmin_s[0], kmax_s[0]);
+      row_interval(prm.mask, i, lo_i, 1, kmin_s[1], kmax_s[1]);
+      long long my_doc = 0;
+      const uint8_t* docs_b = nullptr;
+      if (general) {
+        docs_b = reinterpret_cast<const uint8_t*>(prm.docs) +
+                 (size_t)b * prm.doc_stride_b * (prm.doc_is_i64 ? 8 : 4);
+        if (i < prm.N) {
+          const size_t off = (size_t)i * prm.doc_stride_t;
+          my_doc = prm.doc_is_i64 ? reinterpret_cast<const long long*>(docs_b)[off]
+                                  : (long long)reinterpret_cast<const int*>(docs_b)[off];
+        }
+      }
+
+      float m_run = -1.0e30f;   // running max of raw scores (finite sentinel)
+      float l_run = 0.f;
+      const float c = prm.scale_log2;
+      bool ok = true;
+
+      for (int j = 0; j < n_tiles; ++j) {
+        const TileInfo t = tile_info(s_plan, j);
+        const int sb = j % Cfg::kSBufs;
+        if (!mbar_wait(bar_s_full + 8 * sb, (j / Cfg::kSBufs) & 1, abort_flag, prm.status)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        float s[kTileN];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t r[32];
+          tmem_ld32(tmem + lane_addr + sb * 128 + q4 * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) s[q4 * 32 + e] = __uint_as_float(r[e]);
+        }
+        tc_fence_before();
+        mbar_arrive(bar_s_free + 8 * sb);
+
+        if (t.masked) {
+          const int cmin = kmin_s[t.stream] - t.k0;
+          const int cmax = kmax_s[t.stream] - t.k0;
+#pragma unroll
+          for (int e = 0; e < kTileN; ++e)
+            if (e < cmin || e > cmax) s[e] = -INFINITY;
+          if (general) {
+            // ids are not monotone: compare this row's id with each key's id (uniform loads)
+            uint32_t same[4];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint32_t bits = 0;
+              for (int e = 0; e < 32; ++e) {
+                const int jrow = prm.mask.ks * (t.k0 + q4 * 32 + e) + t.stream;
+                if (jrow >= 0 && jrow < prm.N) {
+                  const size_t off = (size_t)jrow * prm.doc_stride_t;
+                  const long long dk = prm.doc_is_i64
+                                           ? reinterpret_cast<const long long*>(docs_b)[off]
+                                           : (long long)reinterpret_cast<const int*>(docs_b)[off];
+                  bits |= (dk == my_doc ? 1u : 0u) << e;
+                }
+              }
+              same[q4] = bits;
+            }
+#pragma unroll
+            for (int e = 0; e < kTileN; ++e)
+              if (!((same[e >> 5] >> (e & 31)) & 1u)) s[e] = -INFINITY;
+          }
+        }
+        float mx = s[0];
+#pragma unroll
+        for (int e = 1; e < kTileN; ++e) mx = fmaxf(mx, s[e]);
+        const float m_new = fmaxf(m_run, mx);
+        const float alpha = fast_exp2((m_run - m_new) * c);
+        const float neg_mc = -m_new * c;
+        float sum = 0.f;
+        uint32_t pk[kTileN / 2];
+#pragma unroll
+        for (int e = 0; e < kTileN; e += 2) {
+          const float p0 = fast_exp2(fmaf(s[e], c, neg_mc));
+          const float p1 = fast_exp2(fmaf(s[e + 1], c, neg_mc));
+          sum += p0 + p1;
+          pk[e / 2] = pack2<FP16>(p0, p1);
+        }
+        l_run = l_run * alpha + sum;
+        m_run = m_new;
+
+        if (j > 0) {  // P buffer free and O stable once the previous P V product is done
+          if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag, prm.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+        }
+        // P -> shared memory, K-major 128B-swizzled: 16-byte chunk ch of row r sits at
+        // r * 128 + ((ch ^ (r & 7)) << 4) inside each [128 x 64] sub-tile
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint32_t addr = sP + sub * (kTileM * 128) + row * 128 + ((ch ^ (row & 7)) << 4);
+            const int e = sub * 32 + ch * 4;
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[e]),
+                         "r"(pk[e + 1]), "r"(pk[e + 2]), "r"(pk[e + 3])
+                         : "memory");
+          }
+        }
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+          for (int q4 = 0; q4 < D / 32; ++q4) {
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_addr + Cfg::kColO + q4 * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+            tmem_st32(tmem + lane_addr + Cfg::kColO + q4 * 32, r);
+          }
+          tmem_wait_st();
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bar_p_full);
+      }
+
+      // ---------------------------------------------------------------- epilogue
+      if (ok) ok = mbar_wait(bar_pv_done, (n_tiles - 1) & 1, abort_flag, prm.status);
+      if (ok) {
+        tc_fence_after();
+        const float inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
+        uint8_t* o_row = reinterpret_cast<uint8_t*>(prm.o) + ((size_t)bh * prm.N + i) * (D * 2);
+#pragma unroll
+        for (int q4 = 0; q4 < D / 32; ++q4) {
+          uint32_t r[32];
+          tmem_ld32(tmem + lane_addr + Cfg::kColO + q4 * 32, r);
+          tmem_wait_ld();
+          if (i < prm.N) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 u;
+              u.x = pack2<FP16>(__uint_as_float(r[e]) * inv_l, __uint_as_float(r[e + 1]) * inv_l);
+              u.y = pack2<FP16>(__uint_as_float(r[e + 2]) * inv_l, __uint_as_float(r[e + 3]) * inv_l);
+              u.z = pack2<FP16>(__uint_as_float(r[e + 4]) * inv_l, __uint_as_float(r[e + 5]) * inv_l);
+              u.w = pack2<FP16>(__uint_as_float(r[e + 6]) * inv_l, __uint_as_float(r[e + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(o_row + q4 * 64 + e * 2) = u;
+            }
+          }
+        }
+        if (prm.lse != nullptr && i < prm.N)
+          prm.lse[(size_t)bh * prm.N + i] = l_run > 0.f ? m_run * c + log2f(l_run) : -INFINITY;
+        tc_fence_before();
+      }
+    }
+  } else if (!bail && warp < 4) {
+    // nothing visible for any row of this tile: outputs are zero
+    const int i = i0 + tid;
+    if (i < prm.N) {
+      uint4* o_row = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(prm.o) +
+                                              ((size_t)bh * prm.N + i) * (D * 2));
+      for (int e = 0; e < D / 8; ++e) o_row[e] = make_uint4(0, 0, 0, 0);
+      if (prm.lse != nullptr) prm.lse[(size_t)bh * prm.N + i] = -INFINITY;
+    }
+  }
+
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc<Cfg::kTmemCols>(tmem);
+  }
+}
+
+}  // namespace spsattn

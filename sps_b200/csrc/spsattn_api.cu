@@ -1,0 +1,399 @@
+// Host side of libspsattn.so: argument validation, tensor-map encoding, launches.
+// Plain C ABI (include/spsattn.h); no torch types, no allocation, no synchronisation.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "../../include/spsattn.h"
+#include "decode.cuh"
+#include "kv_update.cuh"
+#include "prefill_aux.cuh"
+#include "prefill_sm100.cuh"
+
+using namespace spsattn;
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int clamp_window(long long w, int n) {
+  if (w < 0) return -1;
+  if (w > n) return n;
+  return (int)w;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// workspace layout of the prefill pre-pass: [mono: B ints, padded to 256 B][lo: B*N ints]
+size_t prefill_ws_mono_bytes(int B) { return align_up((size_t)B * sizeof(int), 256); }
+
+MaskParams make_mask(int N, int parity, int w, int pw, int flags) {
+  MaskParams m;
+  m.n_rows = N;
+  m.ks = parity == SPSATTN_PARITY_NONE ? 1 : 2;
+  m.pp = parity == SPSATTN_PARITY_NONE ? -1 : parity;
+  m.w = clamp_window(w, N);
+  m.has_pw = (parity != SPSATTN_PARITY_NONE && pw != SPSATTN_NO_WINDOW) ? 1 : 0;
+  m.pw = m.has_pw ? clamp_window(pw, N) : 0;
+  m.flags = flags;
+  return m;
+}
+
+// Q / O style map: [D, N, BH], box [64, 128, 1]
+int encode_q_map(CUtensorMap* tm, const void* ptr, int BH, int N, int D, int dtype) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return SPSATTN_ERR_DRIVER;
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)N * D * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, dtype == SPSATTN_DTYPE_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                   3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+// K / V map with the two parity streams as a dimension: [D, ks, N/ks, BH], box [64, 1, 128, 1].
+// A tile is 128 consecutive key tokens of one parity; rows of the other parity are skipped by
+// the stride, out-of-range tokens read as zero and the next head is never touched.
+int encode_kv_map(CUtensorMap* tm, const void* ptr, int BH, int N, int D, int ks, int dtype) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return SPSATTN_ERR_DRIVER;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)ks, (cuuint64_t)(N / ks), (cuuint64_t)BH};
+  cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)ks * D * 2, (cuuint64_t)N * D * 2};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, dtype == SPSATTN_DTYPE_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                   4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+template <int D, bool FP16>
+int launch_prefill_sm100(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                         const PrefillParams& prm, cudaStream_t st) {
+  using Cfg = PrefillCfg<D>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(prefill_sm100_kernel<D, FP16>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return (int)attr_err;
+  const long long blocks = (long long)prm.n_qtiles * prm.B * prm.H;
+  if (blocks <= 0 || blocks > 0x7fffffffLL) return SPSATTN_ERR_TOO_LARGE;
+  prefill_sm100_kernel<D, FP16><<<(unsigned)blocks, kPrefillThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, prm);
+  return (int)cudaGetLastError();
+}
+
+int run_doc_prepass(const void* doc_ids, int doc_is_i64, int64_t sb, int64_t stt, int B, int N,
+                    void* workspace, size_t workspace_bytes, int** lo, int** mono, cudaStream_t st) {
+  *lo = nullptr;
+  *mono = nullptr;
+  if (doc_ids == nullptr) return 0;
+  const size_t need = prefill_ws_mono_bytes(B) + (size_t)B * N * sizeof(int);
+  if (workspace == nullptr || workspace_bytes < need) return SPSATTN_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return SPSATTN_ERR_ALIGN;
+  *mono = reinterpret_cast<int*>(workspace);
+  *lo = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + prefill_ws_mono_bytes(B));
+  doc_prepass_kernel<<<B, 1024, 0, st>>>(doc_ids, doc_is_i64, sb, stt, N, *lo, *mono);
+  return (int)cudaGetLastError();
+}
+
+static int decode_chunk_rows(int S, int H, long long max_rows_total) {
+  // large chunks keep the record traffic small; small problems get smaller chunks so that the
+  // grid still fills the 148 SMs several times over
+  int chunk = 512;
+  while (chunk > 128) {
+    const long long blocks = (long long)S * H * ((max_rows_total + chunk - 1) / chunk);
+    if (blocks >= 148LL * 16) break;
+    chunk >>= 1;
+  }
+  return chunk;
+}
+
+static long long decode_max_rows(const spsattn_segment* segs, int n_segments) {
+  long long t = 0;
+  for (int x = 0; x < n_segments; ++x) t += segs[x].max_rows > 0 ? segs[x].max_rows : 0;
+  return t;
+}
+
+template <int D, int NQ, bool FP16>
+static int launch_decode(const DecodeParams& prm, cudaStream_t st) {
+  dim3 grid((unsigned)(prm.S * prm.H), (unsigned)prm.n_chunks);
+  decode_split_kernel<D, NQ, FP16><<<grid, kDecodeThreads, 0, st>>>(prm);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  dim3 mgrid((unsigned)(prm.S * prm.H), NQ);
+  decode_merge_kernel<D, NQ><<<mgrid, D, 0, st>>>(prm);
+  return (int)cudaGetLastError();
+}
+
+template <int D>
+static int launch_decode_d(const DecodeParams& prm, int nq, bool fp16, cudaStream_t st) {
+  if (nq == 1) return fp16 ? launch_decode<D, 1, true>(prm, st) : launch_decode<D, 1, false>(prm, st);
+  return fp16 ? launch_decode<D, 2, true>(prm, st) : launch_decode<D, 2, false>(prm, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int spsattn_version(void) { return 1; }
+
+const char* spsattn_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case SPSATTN_ERR_ARG: return "invalid argument (null pointer, bad enum or bad size)";
+    case SPSATTN_ERR_HEAD_DIM: return "head_dim not supported by this entry point";
+    case SPSATTN_ERR_ALIGN: return "pointer or stride not suitably aligned";
+    case SPSATTN_ERR_WORKSPACE: return "workspace missing or too small";
+    case SPSATTN_ERR_ODD_LENGTH: return "doubled sequence length must be even";
+    case SPSATTN_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable in this driver";
+    case SPSATTN_ERR_TOO_LARGE: return "size beyond a documented maximum";
+    default: break;
+  }
+  if (code > 0) return cudaGetErrorString((cudaError_t)code);
+  return "unknown spsattn error";
+}
+
+size_t spsattn_prefill_workspace_bytes(int B, int H, int N, int D) {
+  (void)H;
+  (void)D;
+  if (B <= 0 || N <= 0) return 256;
+  return prefill_ws_mono_bytes(B) + align_up((size_t)B * N * sizeof(int), 256);
+}
+
+int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                        const void* doc_ids, int doc_is_i64, int64_t doc_stride_b, int64_t doc_stride_t,
+                        int B, int H, int N, int D, int dtype, float sm_scale, int persistent_parity,
+                        int temporary_window, int persistent_window, int mask_flags, void* workspace,
+                        size_t workspace_bytes, int* device_status, void* stream) {
+  if (!q || !k || !v || !o) return SPSATTN_ERR_ARG;
+  if (B <= 0 || H <= 0 || N <= 0) return SPSATTN_ERR_ARG;
+  if (dtype != SPSATTN_DTYPE_BF16 && dtype != SPSATTN_DTYPE_FP16) return SPSATTN_ERR_ARG;
+  if (persistent_parity != SPSATTN_PARITY_EVEN && persistent_parity != SPSATTN_PARITY_ODD &&
+      persistent_parity != SPSATTN_PARITY_NONE)
+    return SPSATTN_ERR_ARG;
+  if (!(sm_scale > 0.f) || !isfinite(sm_scale)) return SPSATTN_ERR_ARG;
+  if (D != 16 && D != 32 && D != 64 && D != 128 && D != 256) return SPSATTN_ERR_HEAD_DIM;
+  if (persistent_parity != SPSATTN_PARITY_NONE && (N & 1)) return SPSATTN_ERR_ODD_LENGTH;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SPSATTN_ERR_ALIGN;
+  if ((long long)B * H > 0x7fffffffLL / 64) return SPSATTN_ERR_TOO_LARGE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+  int *lo = nullptr, *mono = nullptr;
+  int rc = run_doc_prepass(doc_ids, doc_is_i64, doc_stride_b, doc_stride_t, B, N, workspace,
+                           workspace_bytes, &lo, &mono, st);
+  if (rc != 0) return rc;
+
+  const MaskParams mask = make_mask(N, persistent_parity, temporary_window, persistent_window, mask_flags);
+  const float scale_log2 = sm_scale * 1.4426950408889634f;
+  const bool fp16 = dtype == SPSATTN_DTYPE_FP16;
+
+  if (D == 64 || D == 128) {
+    CUtensorMap tq, tk, tv;
+    if ((rc = encode_q_map(&tq, q, B * H, N, D, dtype)) != 0) return rc;
+    if ((rc = encode_kv_map(&tk, k, B * H, N, D, mask.ks, dtype)) != 0) return rc;
+    if ((rc = encode_kv_map(&tv, v, B * H, N, D, mask.ks, dtype)) != 0) return rc;
+    PrefillParams prm;
+    memset(&prm, 0, sizeof(prm));
+    prm.o = o;
+    prm.lse = lse;
+    prm.docs = doc_ids;
+    prm.doc_stride_b = doc_stride_b;
+    prm.doc_stride_t = doc_stride_t;
+    prm.doc_is_i64 = doc_is_i64;
+    prm.lo = lo;
+    prm.mono = mono;
+    prm.B = B;
+    prm.H = H;
+    prm.N = N;
+    prm.n_qtiles = (N + kTileM - 1) / kTileM;
+    prm.mask = mask;
+    prm.scale_log2 = scale_log2;
+    prm.status = device_status;
+    if (D == 64) return fp16 ? launch_prefill_sm100<64, true>(tq, tk, tv, prm, st)
+                             : launch_prefill_sm100<64, false>(tq, tk, tv, prm, st);
+    return fp16 ? launch_prefill_sm100<128, true>(tq, tk, tv, prm, st)
+                : launch_prefill_sm100<128, false>(tq, tk, tv, prm, st);
+  }
+  dim3 grid((N + 3) / 4, B * H);
+  const size_t smem = 4 * (size_t)D * sizeof(float);
+  if (fp16)
+    prefill_generic_kernel<true><<<grid, 128, smem, st>>>(q, k, v, o, lse, doc_ids, doc_is_i64, doc_stride_b,
+                                                          doc_stride_t, lo, mono, H, N, D, mask, scale_log2);
+  else
+    prefill_generic_kernel<false><<<grid, 128, smem, st>>>(q, k, v, o, lse, doc_ids, doc_is_i64, doc_stride_b,
+                                                           doc_stride_t, lo, mono, H, N, D, mask, scale_log2);
+  return (int)cudaGetLastError();
+}
+
+int spsattn_debug_visibility(uint8_t* vis, const void* doc_ids, int doc_is_i64, int64_t doc_stride_b,
+                             int64_t doc_stride_t, int B, int N, int persistent_parity,
+                             int temporary_window, int persistent_window, int mask_flags,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  if (!vis || B <= 0 || N <= 0 || N > 4096) return SPSATTN_ERR_ARG;
+  if (persistent_parity != SPSATTN_PARITY_NONE && (N & 1)) return SPSATTN_ERR_ODD_LENGTH;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int *lo = nullptr, *mono = nullptr;
+  int rc = run_doc_prepass(doc_ids, doc_is_i64, doc_stride_b, doc_stride_t, B, N, workspace,
+                           workspace_bytes, &lo, &mono, st);
+  if (rc != 0) return rc;
+  const MaskParams mask = make_mask(N, persistent_parity, temporary_window, persistent_window, mask_flags);
+  dim3 grid((N + 255) / 256, N, B);
+  visibility_kernel<<<grid, 256, 0, st>>>(vis, doc_ids, doc_is_i64, doc_stride_b, doc_stride_t, lo, mono, N,
+                                          mask);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------ decode
+
+size_t spsattn_decode_workspace_bytes(int S, int H, int D, int nq, const spsattn_segment* segs,
+                                      int n_segments) {
+  if (S <= 0 || H <= 0 || D <= 0 || nq <= 0 || n_segments < 0 || (n_segments > 0 && !segs)) return 256;
+  const long long rows = decode_max_rows(segs, n_segments);
+  const int chunk = decode_chunk_rows(S, H, rows);
+  long long n_chunks = (rows + chunk - 1) / chunk;
+  if (n_chunks < 1) n_chunks = 1;
+  return align_up((size_t)S * H * n_chunks * nq * (D + 2) * sizeof(float), 256);
+}
+
+int spsattn_decode_fwd(const void* q, int nq, float* out, const spsattn_segment* segs, int n_segments,
+                       const spsattn_extra* extras, int n_extras, int S, int H, int D, int dtype,
+                       float sm_scale, void* workspace, size_t workspace_bytes, int* device_status,
+                       void* stream) {
+  (void)device_status;
+  if (!q || !out) return SPSATTN_ERR_ARG;
+  if (nq != 1 && nq != 2) return SPSATTN_ERR_ARG;
+  if (S <= 0 || H <= 0) return SPSATTN_ERR_ARG;
+  if (n_segments < 0 || n_segments > kMaxSegments || (n_segments > 0 && !segs)) return SPSATTN_ERR_ARG;
+  if (n_extras < 0 || n_extras > kMaxExtras || (n_extras > 0 && !extras)) return SPSATTN_ERR_ARG;
+  if (dtype != SPSATTN_DTYPE_BF16 && dtype != SPSATTN_DTYPE_FP16) return SPSATTN_ERR_ARG;
+  if (!isfinite(sm_scale)) return SPSATTN_ERR_ARG;
+  if (D != 8 && D != 16 && D != 32 && D != 64 && D != 128 && D != 256) return SPSATTN_ERR_HEAD_DIM;
+  if (!aligned16(q) || !aligned16(out)) return SPSATTN_ERR_ALIGN;
+  if ((long long)S * H > 0x7fffffffLL) return SPSATTN_ERR_TOO_LARGE;
+
+  DecodeParams prm;
+  memset(&prm, 0, sizeof(prm));
+  for (int x = 0; x < n_segments; ++x) {
+    const spsattn_segment& sg = segs[x];
+    if (!sg.lengths) return SPSATTN_ERR_ARG;
+    if (sg.max_rows > 0 && (!sg.k || !sg.v)) return SPSATTN_ERR_ARG;
+    if (sg.max_rows > 0 && (!aligned16(sg.k) || !aligned16(sg.v))) return SPSATTN_ERR_ALIGN;
+    if ((sg.seq_stride % 8) || (sg.head_stride % 8) || (sg.row_stride % 8) || sg.row_stride < D)
+      return SPSATTN_ERR_ALIGN;
+    DecodeSeg& d = prm.seg[x];
+    d.k = sg.k;
+    d.v = sg.v;
+    d.seq_offset = sg.seq_offset;
+    d.seq_stride = sg.seq_stride;
+    d.head_stride = sg.head_stride;
+    d.row_stride = sg.row_stride;
+    d.lengths = sg.lengths;
+    d.lengths_per_head = sg.lengths_per_head;
+    d.max_rows = sg.max_rows > 0 ? sg.max_rows : 0;
+    d.query_mask = sg.query_mask;
+  }
+  for (int e = 0; e < n_extras; ++e) {
+    if (!extras[e].k || !extras[e].v) return SPSATTN_ERR_ARG;
+    if (!aligned16(extras[e].k) || !aligned16(extras[e].v)) return SPSATTN_ERR_ALIGN;
+    prm.extra_k[e] = extras[e].k;
+    prm.extra_v[e] = extras[e].v;
+    prm.extra_mask[e] = extras[e].query_mask;
+  }
+  const long long rows = decode_max_rows(segs, n_segments);
+  prm.chunk_rows = decode_chunk_rows(S, H, rows);
+  long long n_chunks = (rows + prm.chunk_rows - 1) / prm.chunk_rows;
+  if (n_chunks < 1) n_chunks = 1;
+  if (n_chunks > 65535) return SPSATTN_ERR_TOO_LARGE;
+  prm.n_chunks = (int)n_chunks;
+  const size_t need = (size_t)S * H * n_chunks * nq * (D + 2) * sizeof(float);
+  if (!workspace || workspace_bytes < need) return SPSATTN_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return SPSATTN_ERR_ALIGN;
+  prm.q = q;
+  prm.out = out;
+  prm.partial = reinterpret_cast<float*>(workspace);
+  prm.n_segments = n_segments;
+  prm.n_extras = n_extras;
+  prm.S = S;
+  prm.H = H;
+  prm.nq = nq;
+  prm.scale_log2 = sm_scale * 1.4426950408889634f;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool fp16 = dtype == SPSATTN_DTYPE_FP16;
+  switch (D) {
+    case 8: return launch_decode_d<8>(prm, nq, fp16, st);
+    case 16: return launch_decode_d<16>(prm, nq, fp16, st);
+    case 32: return launch_decode_d<32>(prm, nq, fp16, st);
+    case 64: return launch_decode_d<64>(prm, nq, fp16, st);
+    case 128: return launch_decode_d<128>(prm, nq, fp16, st);
+    default: return launch_decode_d<256>(prm, nq, fp16, st);
+  }
+}
+
+// --------------------------------------------------------------------------------------- kv update
+
+int spsattn_kv_update(void* nw_k, void* nw_v, int64_t* nw_len, int64_t* nw_pos, void* br_k, void* br_v,
+                      int64_t* br_len, const void* k_window, const void* v_window, const void* k_retained,
+                      const void* v_retained, const int8_t* active, int S, int H, int D,
+                      int window_storage, int retained_storage, int window_tokens, int elem_bytes,
+                      void* stream) {
+  if (!br_k || !br_v || !br_len || !k_retained || !v_retained || !active) return SPSATTN_ERR_ARG;
+  if (S <= 0 || H <= 0 || D <= 0 || retained_storage < 0) return SPSATTN_ERR_ARG;
+  if (elem_bytes != 2 && elem_bytes != 4) return SPSATTN_ERR_ARG;
+  if ((D * elem_bytes) % 4) return SPSATTN_ERR_ALIGN;
+  if (window_tokens > 0) {
+    if (!nw_k || !nw_v || !nw_len || !nw_pos || !k_window || !v_window) return SPSATTN_ERR_ARG;
+    if (window_storage <= 0) return SPSATTN_ERR_ARG;
+  }
+  KvUpdateParams p;
+  p.nw_k = reinterpret_cast<uint32_t*>(nw_k);
+  p.nw_v = reinterpret_cast<uint32_t*>(nw_v);
+  p.nw_len = nw_len;
+  p.nw_pos = nw_pos;
+  p.br_k = reinterpret_cast<uint32_t*>(br_k);
+  p.br_v = reinterpret_cast<uint32_t*>(br_v);
+  p.br_len = br_len;
+  p.k_window = reinterpret_cast<const uint32_t*>(k_window);
+  p.v_window = reinterpret_cast<const uint32_t*>(v_window);
+  p.k_retained = reinterpret_cast<const uint32_t*>(k_retained);
+  p.v_retained = reinterpret_cast<const uint32_t*>(v_retained);
+  p.active = active;
+  p.H = H;
+  p.row_words = D * elem_bytes / 4;
+  p.window_storage = window_storage;
+  p.retained_storage = retained_storage;
+  p.window_tokens = window_tokens > 0 ? window_tokens : 0;
+  kv_update_kernel<<<S, 256, (size_t)H * sizeof(long long), reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

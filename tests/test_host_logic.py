@@ -1,0 +1,155 @@
+"""Host-side logic that needs no GPU: the C-ABI library loads and exports what the header
+declares, argument errors are caught before any launch, the key-tile planner and the workload
+arithmetic agree with the oracle's exhaustive counts."""
+
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import sps_oracle as orc
+from sps_b200 import _lib, workloads
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    header = open(os.path.join(ROOT, "include", "spsattn.h")).read()
+    declared = set(re.findall(r"\b(spsattn_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(_lib.EXPORTS)
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert lib.spsattn_version() >= 1
+
+
+def test_argument_errors_are_reported_before_any_launch():
+    lib = _lib.load()
+    err = lambda c: lib.spsattn_strerror(c).decode()
+    # null pointers / bad sizes never reach CUDA
+    rc = lib.spsattn_prefill_fwd(None, None, None, None, None, None, 0, 0, 0, 1, 1, 8, 64, 0, 0.125,
+                                 0, 1, _lib.NO_WINDOW, 0, None, 0, None, None)
+    assert rc == -1 and "invalid argument" in err(rc)
+    fake = ctypes.c_void_p(4096)
+    args = lambda **kw: [fake, fake, fake, fake, None, None, 0, 0, 0, kw.get("B", 1), 1, kw.get("N", 8),
+                         kw.get("D", 64), kw.get("dtype", 0), kw.get("scale", 0.125), kw.get("parity", 0), 1,
+                         _lib.NO_WINDOW, 0, None, 0, None, None]
+    assert lib.spsattn_prefill_fwd(*args(D=48)) == -2
+    assert lib.spsattn_prefill_fwd(*args(N=7)) == -5
+    assert lib.spsattn_prefill_fwd(*args(scale=0.0)) == -1
+    assert lib.spsattn_prefill_fwd(*args(dtype=5)) == -1
+    assert lib.spsattn_prefill_fwd(*args(parity=3)) == -1
+    bad = ctypes.c_void_p(4100)
+    a = args()
+    a[0] = bad
+    assert lib.spsattn_prefill_fwd(*a) == -3
+    assert lib.spsattn_decode_fwd(None, 2, None, None, 0, None, 0, 1, 1, 64, 0, 0.125, None, 0, None, None) == -1
+    assert lib.spsattn_decode_fwd(fake, 3, fake, None, 0, None, 0, 1, 1, 64, 0, 0.125, None, 0, None, None) == -1
+    assert lib.spsattn_decode_fwd(fake, 2, fake, None, 0, None, 0, 1, 1, 24, 0, 0.125, None, 0, None, None) == -2
+    # missing workspace
+    assert lib.spsattn_decode_fwd(fake, 2, fake, None, 0, None, 0, 1, 1, 64, 0, 0.125, None, 0, None, None) == -4
+    assert lib.spsattn_kv_update(*([None] * 12), 1, 1, 64, 0, 4, 0, 2, None) == -1
+    assert "unknown" not in err(-7)
+
+
+def test_workspace_sizes():
+    lib = _lib.load()
+    assert lib.spsattn_prefill_workspace_bytes(8, 12, 8192, 64) >= 8 * 8192 * 4 + 8 * 4
+    seg = (_lib.Segment * 2)()
+    seg[0].max_rows, seg[1].max_rows = 64, 4096
+    need = lib.spsattn_decode_workspace_bytes(128, 16, 64, 2, seg, 2)
+    chunks = -(-4160 // 512)
+    assert need >= 128 * 16 * chunks * 2 * 66 * 4
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libspsattn.so")
+    with pytest.raises(_lib.SpsAttnError):
+        _lib.load()
+
+
+def test_cpu_tensors_are_refused():
+    import sps_b200
+    q = torch.randn(1, 1, 8, 64).bfloat16()
+    with pytest.raises(RuntimeError):
+        sps_b200.sps_sliding_attention(q, q, q, 0.125, 2)
+    with pytest.raises(RuntimeError):
+        sps_b200.decode_attention(torch.randn(1, 2, 1, 64).bfloat16(), [], [])
+
+
+def test_closed_form_pair_counts_match_exhaustive_count():
+    docs = workloads.geometric_docs(2, 256, 100, 0)
+    assert workloads.useful_pairs(docs, 64) == orc.count_visible_pairs(docs, 512, 2, temporary_window=64) == 80266
+    # the prose variant of the rule: input queries skip the predict stream, exclusive window
+    want = orc.count_visible_pairs(docs, 512, 2, temporary_window=63,
+                                   mask_flags=orc.FLAG_PERSISTENT_Q_SKIPS_TEMPORARY)
+    assert workloads.useful_pairs(docs, 64, "baseline_prose") == want == 61432
+    docs = workloads.geometric_docs(3, 300, 40, 5)
+    assert workloads.useful_pairs(docs, 7) == orc.count_visible_pairs(docs, 600, 3, temporary_window=7)
+
+
+def test_benchmark_work_figures():
+    B, H, T, D, w, mean = workloads.PREFILL_CONFIGS["cfg1_s_scale"]
+    pairs = workloads.useful_pairs(workloads.geometric_docs(B, T, mean, 0), w)
+    assert pairs == 55671620 and abs(workloads.prefill_flops(pairs, H, D) / 1e9 - 171.02) < 0.01
+    B, H, T, D, w, mean = workloads.PREFILL_CONFIGS["cfg4_full_window"]
+    assert workloads.useful_pairs(workloads.geometric_docs(B, T, mean, 0), w) == 134234112
+    lens = workloads.decode_lengths("cfg2_segmented_decode")
+    assert int(lens.sum()) == 299847
+    assert abs(workloads.decode_bytes(lens, 64, 16, 64) / 1e6 - 1264.35) < 0.01
+
+
+def test_shard_slices_cover_everything_once():
+    for n, world in ((8, 1), (8, 2), (8, 8), (128, 3), (16, 4), (5, 8)):
+        seen = []
+        for r in range(world):
+            seen += list(range(n)[workloads.shard_slice(n, r, world)])
+        assert seen == list(range(n))
+
+
+def _host_intervals(n, parity, w, pw, flags, docs_row):
+    """The kernels' per-row interval rule, restated on the host from csrc/mask.cuh."""
+    lo = orc.run_starts(docs_row) if docs_row is not None else np.zeros(n, dtype=np.int64)
+    vis = np.zeros((n, n), dtype=bool)
+    ks = 1 if parity == -1 else 2
+    for i in range(n):
+        for p in range(ks):
+            if ks == 1:
+                kmin, kmax = int(lo[i]), i
+            else:
+                kmax = (i - p) >> 1
+                kmin = (int(lo[i]) - p + 1) >> 1
+                ti = i >> 1
+                if p == parity:
+                    if pw is not None:
+                        if pw >= 0:
+                            kmin = max(kmin, ti - pw)
+                        elif (i & 1) == p:
+                            kmin = kmax = ti
+                        else:
+                            kmin, kmax = 0, -1
+                else:
+                    kmin = max(kmin, ti - w)
+                    if (flags & 1) and (i & 1) == parity:
+                        kmin, kmax = 0, -1
+            for kt in range(max(kmin, 0), kmax + 1):
+                vis[i, ks * kt + p] = True
+    return vis
+
+
+@pytest.mark.parametrize("parity", [0, 1, -1])
+def test_interval_rule_equals_reference_rule(parity):
+    rng = np.random.default_rng(parity + 3)
+    for n, w, pw, flags in ((8, 0, None, 0), (30, 2, None, 0), (64, 5, 1, 0), (40, 3, -1, 0), (50, 4, None, 1),
+                            (36, -1, 0, 0), (20, 100, None, 0)):
+        if parity == -1 and (pw is not None or flags):
+            continue
+        for docs in (None, np.cumsum(rng.random(n) < 0.15).astype(np.int64)):
+            got = _host_intervals(n, parity, w, pw, flags, docs)
+            want = orc.visible_mask(n, persistent_parity=parity, temporary_window=w, persistent_window=pw,
+                                    mask_flags=flags, docs_row=docs)
+            assert np.array_equal(got, want), (n, w, pw, flags)
