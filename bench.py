@@ -256,6 +256,35 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """Small single-kernel cases for profiler captures (a few hundred MB on the device, inputs
+    still larger than L2): `prefill-small` = 4 of the 8 batch rows of the s-scale prefill,
+    `decode-small` = 32 of the 128 decode sequences.  Prints a short JSON line, not the
+    benchmark contract line."""
+    import sps_b200
+    from sps_b200 import workloads
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    if args.case == "prefill-small":
+        wl = workloads.make_prefill(PREFILL, device, batch_slice=slice(0, 4))
+        out = torch.empty_like(wl.q)
+        fn = lambda: sps_b200.prefill_attention(wl.q, wl.k, wl.v, wl.sm_scale, persistent_parity=0,
+                                                temporary_window=wl.window, documents_idx=wl.docs, out=out)
+        work, unit = wl.flops / 1e12, "TFLOP/s"
+    else:
+        dw = workloads.make_decode(DECODE, device, seq_slice=slice(0, 32))
+        segs = [sps_b200.KVSegment(dw.ring_k, dw.ring_v, dw.ring_len, max_len_cap=dw.ring_k.shape[2]),
+                sps_b200.KVSegment(dw.cache_k, dw.cache_v, dw.cache_len, max_len_cap=dw.cache_k.shape[2])]
+        fn = lambda: sps_b200.segmented_q2_attention(
+            dw.q, segs, current_normal_k_BxHxD=dw.cur_k, current_normal_v_BxHxD=dw.cur_v,
+            current_predict_k_BxHxD=dw.pred_k, current_predict_v_BxHxD=dw.pred_v, attn_dtype=torch.bfloat16)
+        work, unit = dw.bytes / 1e9, "GB/s"
+    _, launch_ms = timed_steps(fn, args.steps, max(args.warmup, 1), 1, device)
+    sps_b200.check_device_status(device)
+    print(json.dumps({"case": args.case, "launch_ms": launch_ms, "work": work,
+                      "achieved": work / (launch_ms * 1e-3), "unit": unit}))
+
+
 def _sum_over_ranks(x, world, device):
     import torch.distributed as dist
     t = torch.tensor([x], dtype=torch.float64, device=device)
@@ -338,12 +367,15 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--case", choices=["full", "prefill-small", "decode-small"], default="full")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-decode", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.case != "full":
+        run_case(args)
     else:
         run_ours(args)
 
