@@ -52,6 +52,7 @@ extern "C" {
 #define SPSATTN_ERR_ODD_LENGTH (-5) /* doubled sequence length must be even */
 #define SPSATTN_ERR_DRIVER (-6)     /* tensor-map encoder unavailable */
 #define SPSATTN_ERR_TOO_LARGE (-7)  /* size beyond a documented maximum */
+#define SPSATTN_ERR_SCRATCH_LIMIT (-8) /* needs more scratch than the built-in static buffer holds */
 
 /* device_status codes written by kernels (0 = ok) */
 #define SPSATTN_STATUS_WAIT_EXPIRED 1
@@ -131,6 +132,37 @@ int spsattn_decode_fwd(const void* q, int nq, float* out,
                        int S, int H, int D, int dtype, float sm_scale,
                        void* workspace, size_t workspace_bytes,
                        int* device_status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Allocation-free decode (no counterpart in the reference: its wrappers allocate freely through
+ * torch).  Same computation, arguments and result as spsattn_decode_fwd, but the split-K records
+ * go to a buffer that is compiled into the library instead of a caller-supplied workspace, so the
+ * call needs no device allocation from anybody.  It is meant for hosts that cannot allocate at
+ * the point where they decode: a serving process whose cache manager has already claimed all of
+ * device memory for its own arena (a fresh cudaMalloc would fail or shrink the arena), a step
+ * loop that must not hit cudaMalloc's device-wide synchronisation, or a binding that reaches the
+ * library through an FFI and has no allocator to hand over.
+ *
+ * Limit: the records of one call, spsattn_decode_workspace_bytes(...), must fit in
+ * SPSATTN_NOALLOC_SCRATCH_BYTES (16 MiB; the benchmark's 128-sequence step needs 9.3 MiB).  A larger
+ * problem is refused with SPSATTN_ERR_SCRATCH_LIMIT before anything is launched: split the
+ * sequences over several calls or use spsattn_decode_fwd.  Every GPU that loads the library
+ * carries the 16 MiB until the process exits.
+ *
+ * The first call on each device looks up the buffer's device address (the device must be
+ * current, as for every call); make that first call outside any stream capture.  All calls on a
+ * device share the one buffer: calls that can overlap on the GPU (different streams, no ordering
+ * between them) race on it and must be serialised by the caller.  The buffer keeps the previous
+ * call's records; nothing in it has to start at zero, because a call only reads records it has
+ * written itself.  The entry point calls no cudaMalloc / cudaFree and no allocating library routine.
+ * ------------------------------------------------------------------------------------------- */
+#define SPSATTN_NOALLOC_SCRATCH_BYTES (16u << 20)
+
+int spsattn_decode_fwd_noalloc(const void* q, int nq, float* out,
+                               const spsattn_segment* segs, int n_segments,
+                               const spsattn_extra* extras, int n_extras,
+                               int S, int H, int D, int dtype, float sm_scale,
+                               int* device_status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Decode KV-cache update, in place (decode_attention_fast.py:34-136): for every active sequence

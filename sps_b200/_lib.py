@@ -15,12 +15,13 @@ LIB_PATH = os.path.join(_HERE, "libspsattn.so")
 DTYPE_BF16, DTYPE_FP16 = 0, 1
 PARITY_EVEN, PARITY_ODD, PARITY_NONE = 0, 1, -1
 NO_WINDOW = -2147483648
+NOALLOC_SCRATCH_BYTES = 16 << 20
 FLAG_PERSISTENT_Q_SKIPS_TEMPORARY = 1
 
 EXPORTS = (
     "spsattn_version", "spsattn_strerror",
     "spsattn_prefill_workspace_bytes", "spsattn_prefill_fwd",
-    "spsattn_decode_workspace_bytes", "spsattn_decode_fwd",
+    "spsattn_decode_workspace_bytes", "spsattn_decode_fwd", "spsattn_decode_fwd_noalloc",
     "spsattn_kv_update", "spsattn_debug_visibility",
 )
 
@@ -72,6 +73,9 @@ def load() -> C.CDLL:
     lib.spsattn_decode_fwd.restype = i32
     lib.spsattn_decode_fwd.argtypes = [vp, i32, vp, C.POINTER(Segment), i32, C.POINTER(Extra), i32,
                                        i32, i32, i32, i32, f32, vp, sz, vp, vp]
+    lib.spsattn_decode_fwd_noalloc.restype = i32
+    lib.spsattn_decode_fwd_noalloc.argtypes = [vp, i32, vp, C.POINTER(Segment), i32, C.POINTER(Extra), i32,
+                                               i32, i32, i32, i32, f32, vp, vp]
     lib.spsattn_kv_update.restype = i32
     lib.spsattn_kv_update.argtypes = [vp] * 12 + [i32] * 7 + [vp]
     lib.spsattn_debug_visibility.restype = i32

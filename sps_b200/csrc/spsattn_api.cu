@@ -177,6 +177,10 @@ const char* spsattn_strerror(int code) {
     case SPSATTN_ERR_ODD_LENGTH: return "doubled sequence length must be even";
     case SPSATTN_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable in this driver";
     case SPSATTN_ERR_TOO_LARGE: return "size beyond a documented maximum";
+    case SPSATTN_ERR_SCRATCH_LIMIT:
+      return "the split-K records of this call exceed the built-in 16 MiB scratch buffer "
+             "(SPSATTN_NOALLOC_SCRATCH_BYTES); split the sequences over several calls or use "
+             "spsattn_decode_fwd with a caller-owned workspace";
     default: break;
   }
   if (code > 0) return cudaGetErrorString((cudaError_t)code);
@@ -357,6 +361,50 @@ int spsattn_decode_fwd(const void* q, int nq, float* out, const spsattn_segment*
     case 128: return launch_decode_d<128>(prm, nq, fp16, st);
     default: return launch_decode_d<256>(prm, nq, fp16, st);
   }
+}
+
+// ------------------------------------------------------------------------- allocation-free decode
+// Scratch for spsattn_decode_fwd_noalloc: lives in the library image, one copy per device that
+// loads it.  In host code the name below is only a handle for cudaGetSymbolAddress, never a
+// device address; kernels receive the looked-up pointer.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[SPSATTN_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+void* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+
+// Device address of the scratch buffer on the current device; looked up once per device.
+int noalloc_scratch_ptr(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return SPSATTN_ERR_TOO_LARGE;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (ptr == nullptr) return SPSATTN_ERR_ARG;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+int spsattn_decode_fwd_noalloc(const void* q, int nq, float* out, const spsattn_segment* segs,
+                               int n_segments, const spsattn_extra* extras, int n_extras, int S, int H,
+                               int D, int dtype, float sm_scale, int* device_status, void* stream) {
+  if (S <= 0 || H <= 0 || D <= 0 || (nq != 1 && nq != 2)) return SPSATTN_ERR_ARG;
+  if (n_segments < 0 || n_segments > kMaxSegments || (n_segments > 0 && !segs)) return SPSATTN_ERR_ARG;
+  const size_t need = spsattn_decode_workspace_bytes(S, H, D, nq, segs, n_segments);
+  if (need > (size_t)SPSATTN_NOALLOC_SCRATCH_BYTES) return SPSATTN_ERR_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  const int rc = noalloc_scratch_ptr(&scratch);
+  if (rc != 0) return rc;
+  return spsattn_decode_fwd(q, nq, out, segs, n_segments, extras, n_extras, S, H, D, dtype, sm_scale,
+                            scratch, (size_t)SPSATTN_NOALLOC_SCRATCH_BYTES, device_status, stream);
 }
 
 // --------------------------------------------------------------------------------------- kv update
