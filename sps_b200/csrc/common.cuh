@@ -25,6 +25,25 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// max of three (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 2^x on a packed pair of 16-bit floats (one special-function instruction for two elements)
+template <bool FP16>
+__device__ __forceinline__ uint32_t exp2_packed(uint32_t x) {
+  uint32_t y;
+  if constexpr (FP16) {
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  } else {
+    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(y) : "r"(x));
+  }
+  return y;
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -34,7 +34,21 @@ struct PrefillParams {
   MaskParams mask;
   float scale_log2;      // sm_scale * log2(e)
   int* status;
+  long long* trace;      // cycle stamps (only read by builds with -DSPSATTN_TRACE), else null
 };
+
+// Optional per-block cycle stamps for tuning: compiled out unless SPSATTN_TRACE is defined.
+// Layout: [block][tile < kTraceTiles][slot < 16] of clock64().
+constexpr int kTraceTiles = 40;
+#ifdef SPSATTN_TRACE
+#define SPS_TRACE(tile, slot)                                                                  \
+  do {                                                                                         \
+    if (prm.trace != nullptr && blockIdx.x < 4096 && (tile) < kTraceTiles)                     \
+      prm.trace[((size_t)blockIdx.x * kTraceTiles + (tile)) * 16 + (slot)] = clock64();        \
+  } while (0)
+#else
+#define SPS_TRACE(tile, slot) do { } while (0)
+#endif
 
 constexpr int kTileM = 128;      // query rows per block
 constexpr int kTileN = 128;      // key tokens per tile
@@ -87,7 +101,9 @@ __device__ __forceinline__ TileInfo tile_info(const BlockPlan& bp, int j) {
   return t;
 }
 
-template <int D, bool FP16>
+constexpr float kRescaleLog2 = 8.0f;
+
+template <int D, bool FP16, bool PACKED_EXP>
 __global__ void __launch_bounds__(kPrefillThreads, PrefillCfg<D>::kBlocksPerSM)
 prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const PrefillParams prm) {
@@ -100,6 +116,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  if (tid == 0) SPS_TRACE(0, 15);
 
   // heavy query tiles (late rows) first, all tiles of one (b,h) adjacent so K/V stay in L2
   const int bh = blockIdx.x / prm.n_qtiles;
@@ -154,20 +171,30 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     bp.n_tiles = bp.sp[0].ntiles + bp.sp[1].ntiles;
     s_plan = bp;
 
-    mbar_init(bar_q_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_k_full + 8 * s, 1);
-      mbar_init(bar_k_empty + 8 * s, 1);
-      mbar_init(bar_v_full + 8 * s, 1);
-      mbar_init(bar_v_empty + 8 * s, 1);
-      mbar_init(bar_s_full + 8 * s, 1);
-      mbar_init(bar_s_free + 8 * s, 128);
-    }
-    mbar_init(bar_p_full, 128);
-    mbar_init(bar_pv_done, 1);
-    fence_barrier_init();
   }
   if (warp == 4) {
+    if (lane == 0) {
+      mbar_init(bar_q_full, 1);
+      for (int s = 0; s < 2; ++s) {
+        mbar_init(bar_k_full + 8 * s, 1);
+        mbar_init(bar_k_empty + 8 * s, 1);
+        mbar_init(bar_v_full + 8 * s, 1);
+        mbar_init(bar_v_empty + 8 * s, 1);
+        mbar_init(bar_s_full + 8 * s, 1);
+        mbar_init(bar_s_free + 8 * s, 128);
+      }
+      mbar_init(bar_p_full, 128);
+      mbar_init(bar_pv_done, 1);
+      fence_barrier_init();
+      // the Q tile depends on nothing but the block index: start it before the plan is known
+      tma_prefetch_desc(&tm_q);
+      mbar_arrive_expect_tx(bar_q_full, Cfg::kTileBytes);
+      for (int c = 0; c < D / 64; ++c)
+        tma_load_3d(sQ + c * Cfg::kSubTileBytes, &tm_q, bar_q_full, c * 64, i0, bh);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+    }
+    __syncwarp();
     tmem_alloc<Cfg::kTmemCols>(smem_u32(&s_tmem_base));
     tmem_relinquish();
   }
@@ -177,6 +204,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   const uint32_t tmem = s_tmem_base;
   const int n_tiles = s_plan.n_tiles;
+  if (tid == 0) SPS_TRACE(1, 15);
   volatile int* abort_flag = &s_abort;
   const bool bail = s_abort != 0;
 
@@ -184,12 +212,6 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (warp == 4) {
       // ------------------------------------------------------------------ TMA producer
       if (lane == 0) {
-        tma_prefetch_desc(&tm_q);
-        tma_prefetch_desc(&tm_k);
-        tma_prefetch_desc(&tm_v);
-        mbar_arrive_expect_tx(bar_q_full, Cfg::kTileBytes);
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_3d(sQ + c * Cfg::kSubTileBytes, &tm_q, bar_q_full, c * 64, i0, bh);
         auto load_k = [&](int j) {
           const TileInfo t = tile_info(s_plan, j);
           const int st = j % Cfg::kStagesK;
@@ -201,6 +223,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int c = 0; c < D / 64; ++c)
             tma_load_4d(sK + st * Cfg::kTileBytes + c * Cfg::kSubTileBytes, &tm_k, bar_k_full + 8 * st,
                         c * 64, t.stream, t.k0, bh);
+          SPS_TRACE(j, 13);
           return true;
         };
         auto load_v = [&](int j) {
@@ -214,6 +237,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int c = 0; c < D / 64; ++c)
             tma_load_4d(sV + st * Cfg::kTileBytes + c * Cfg::kSubTileBytes, &tm_v, bar_v_full + 8 * st,
                         c * 64, t.stream, t.k0, bh);
+          SPS_TRACE(j, 14);
           return true;
         };
         bool ok = load_k(0);
@@ -228,6 +252,11 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (lane == 0) {
         constexpr uint32_t idesc_qk = make_idesc_f16(FP16, kTileM, kTileN, false, false);
         constexpr uint32_t idesc_pv = make_idesc_f16(FP16, kTileM, D, false, true);
+        // descriptors differ from tile to tile only in the start-address field (low 14 bits)
+        const uint64_t desc_q0 = make_smem_desc_sw128(sQ, 16, 1024);
+        const uint64_t desc_k0 = make_smem_desc_sw128(sK, 16, 1024);
+        const uint64_t desc_p0 = make_smem_desc_sw128(sP, 16, 1024);
+        const uint64_t desc_v0 = make_smem_desc_sw128(sV, Cfg::kSubTileBytes, 1024);
         auto issue_qk = [&](int j) {
           const int st = j % Cfg::kStagesK;
           const int sb = j % Cfg::kSBufs;
@@ -237,15 +266,16 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
               return false;
           }
           tc_fence_after();
+          const uint64_t db0 = desc_k0 + (uint64_t)((st * Cfg::kTileBytes) >> 4);
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t off = (kk / 4) * Cfg::kSubTileBytes + (kk % 4) * 32;
-            const uint64_t da = make_smem_desc_sw128(sQ + off, 16, 1024);
-            const uint64_t db = make_smem_desc_sw128(sK + st * Cfg::kTileBytes + off, 16, 1024);
-            umma_ss(tmem + sb * 128, da, db, idesc_qk, kk > 0 ? 1u : 0u);
+            // a K step of 16 elements is 32 bytes inside a 128-byte row; 64 elements per sub-tile
+            const uint64_t off = (uint64_t)(((kk / 4) * Cfg::kSubTileBytes + (kk % 4) * 32) >> 4);
+            umma_ss(tmem + sb * 128, desc_q0 + off, db0 + off, idesc_qk, kk > 0 ? 1u : 0u);
           }
           umma_commit(bar_s_full + 8 * sb);
           umma_commit(bar_k_empty + 8 * st);
+          SPS_TRACE(j, 9);
           return true;
         };
         bool ok = mbar_wait(bar_q_full, 0, abort_flag, prm.status);
@@ -255,19 +285,21 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           if (!ok) break;
           const int st = j % Cfg::kStagesV;
           if (!mbar_wait(bar_p_full, j & 1, abort_flag, prm.status)) break;
+          SPS_TRACE(j, 10);
           if (!mbar_wait(bar_v_full + 8 * st, (j / Cfg::kStagesV) & 1, abort_flag, prm.status)) break;
+          SPS_TRACE(j, 11);
           tc_fence_after();
+          const uint64_t dv0 = desc_v0 + (uint64_t)((st * Cfg::kTileBytes) >> 4);
 #pragma unroll
           for (int kk = 0; kk < kTileN / 16; ++kk) {
             // P: K-major, two 64-key sub-tiles; V: MN-major, 16 key rows = 2048 bytes per step
-            const uint64_t da =
-                make_smem_desc_sw128(sP + (kk / 4) * (kTileM * 128) + (kk % 4) * 32, 16, 1024);
-            const uint64_t db = make_smem_desc_sw128(sV + st * Cfg::kTileBytes + kk * 2048,
-                                                     Cfg::kSubTileBytes, 1024);
-            umma_ss(tmem + Cfg::kColO, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+            const uint64_t pa = (uint64_t)(((kk / 4) * (kTileM * 128) + (kk % 4) * 32) >> 4);
+            umma_ss(tmem + Cfg::kColO, desc_p0 + pa, dv0 + (uint64_t)((kk * 2048) >> 4), idesc_pv,
+                    (j > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(bar_pv_done);
           umma_commit(bar_v_empty + 8 * st);
+          SPS_TRACE(j, 12);
         }
       }
       __syncwarp();
@@ -302,22 +334,32 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       for (int j = 0; j < n_tiles; ++j) {
         const TileInfo t = tile_info(s_plan, j);
         const int sb = j % Cfg::kSBufs;
+        if (tid == 0) SPS_TRACE(j, 0);
         if (!mbar_wait(bar_s_full + 8 * sb, (j / Cfg::kSBufs) & 1, abort_flag, prm.status)) {
           ok = false;
           break;
         }
+        if (tid == 0) SPS_TRACE(j, 1);
         tc_fence_after();
         float s[kTileN];
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint32_t r[32];
-          tmem_ld32(tmem + lane_addr + sb * 128 + q4 * 32, r);
+        {
+          uint32_t r0[32], r1[32], r2[32], r3[32];
+          tmem_ld32(tmem + lane_addr + sb * 128, r0);
+          tmem_ld32(tmem + lane_addr + sb * 128 + 32, r1);
+          tmem_ld32(tmem + lane_addr + sb * 128 + 64, r2);
+          tmem_ld32(tmem + lane_addr + sb * 128 + 96, r3);
           tmem_wait_ld();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) s[q4 * 32 + e] = __uint_as_float(r[e]);
+          for (int e = 0; e < 32; ++e) {
+            s[e] = __uint_as_float(r0[e]);
+            s[32 + e] = __uint_as_float(r1[e]);
+            s[64 + e] = __uint_as_float(r2[e]);
+            s[96 + e] = __uint_as_float(r3[e]);
+          }
         }
         tc_fence_before();
         mbar_arrive(bar_s_free + 8 * sb);
+        if (tid == 0) SPS_TRACE(j, 2);
 
         if (t.masked) {
           const int cmin = kmin_s[t.stream] - t.k0;
@@ -348,23 +390,54 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
               if (!((same[e >> 5] >> (e & 31)) & 1u)) s[e] = -INFINITY;
           }
         }
-        float mx = s[0];
+        float mx;
+        {
+          float m4[4];
 #pragma unroll
-        for (int e = 1; e < kTileN; ++e) mx = fmaxf(mx, s[e]);
-        const float m_new = fmaxf(m_run, mx);
-        const float alpha = fast_exp2((m_run - m_new) * c);
-        const float neg_mc = -m_new * c;
-        float sum = 0.f;
+          for (int x = 0; x < 4; ++x) m4[x] = fmax3(s[x], s[4 + x], s[8 + x]);
+#pragma unroll
+          for (int e = 12; e + 8 <= kTileN; e += 8) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) m4[x] = fmax3(m4[x], s[e + x], s[e + 4 + x]);
+          }
+#pragma unroll
+          for (int x = 0; x < 4; ++x) m4[x] = fmaxf(m4[x], s[kTileN - 4 + x]);
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        }
+        if (tid == 0) SPS_TRACE(j, 3);
+        // Lazy rescaling: the exponent offset m_run only moves when some row of the warp grew by
+        // more than 2^kRescaleLog2; until then P may exceed 1 (by at most that factor), which
+        // fp32 accumulation and the final division by l absorb exactly.
+        float alpha = 1.0f;
+        const bool grow = (mx - m_run) * c > kRescaleLog2;
+        const bool rescale = __any_sync(0xffffffffu, grow);
+        if (rescale) {
+          const float m_new = fmaxf(m_run, mx);
+          alpha = fast_exp2((m_run - m_new) * c);
+          l_run *= alpha;
+          m_run = m_new;
+        }
+        const float neg_mc = -m_run * c;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[kTileN / 2];
 #pragma unroll
         for (int e = 0; e < kTileN; e += 2) {
-          const float p0 = fast_exp2(fmaf(s[e], c, neg_mc));
-          const float p1 = fast_exp2(fmaf(s[e + 1], c, neg_mc));
-          sum += p0 + p1;
-          pk[e / 2] = pack2<FP16>(p0, p1);
+          if constexpr (PACKED_EXP) {
+            const uint32_t xp = pack2<FP16>(fmaf(s[e], c, neg_mc), fmaf(s[e + 1], c, neg_mc));
+            const uint32_t pp = exp2_packed<FP16>(xp);
+            float p0, p1;
+            unpack2<FP16>(pp, p0, p1);
+            sum4[(e / 2) & 3] += p0 + p1;
+            pk[e / 2] = pp;
+          } else {
+            const float p0 = fast_exp2(fmaf(s[e], c, neg_mc));
+            const float p1 = fast_exp2(fmaf(s[e + 1], c, neg_mc));
+            sum4[(e / 2) & 3] += p0 + p1;
+            pk[e / 2] = pack2<FP16>(p0, p1);
+          }
         }
-        l_run = l_run * alpha + sum;
-        m_run = m_new;
+        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        if (tid == 0) SPS_TRACE(j, 4);
 
         if (j > 0) {  // P buffer free and O stable once the previous P V product is done
           if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag, prm.status)) {
@@ -373,6 +446,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
           tc_fence_after();
         }
+        if (tid == 0) SPS_TRACE(j, 5);
         // P -> shared memory, K-major 128B-swizzled: 16-byte chunk ch of row r sits at
         // r * 128 + ((ch ^ (r & 7)) << 4) inside each [128 x 64] sub-tile
 #pragma unroll
@@ -386,7 +460,8 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                          : "memory");
           }
         }
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+        if (tid == 0) SPS_TRACE(j, 6);
+        if (j > 0 && rescale) {
 #pragma unroll
           for (int q4 = 0; q4 < D / 32; ++q4) {
             uint32_t r[32];
@@ -398,9 +473,11 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
           tmem_wait_st();
         }
+        if (tid == 0) SPS_TRACE(j, 7);
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(bar_p_full);
+        if (tid == 0) SPS_TRACE(j, 8);
       }
 
       // ---------------------------------------------------------------- epilogue
@@ -442,7 +519,10 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
   }
 
+  // the Q tile load was started before the plan was known: never leave with it in flight
+  if (warp == 4 && lane == 0) mbar_wait(bar_q_full, 0, abort_flag, prm.status);
   __syncthreads();
+  if (tid == 0) SPS_TRACE(2, 15);
   if (warp == 4) {
     tc_fence_after();
     tmem_dealloc<Cfg::kTmemCols>(tmem);

@@ -95,6 +95,10 @@ int encode_kv_map(CUtensorMap* tm, const void* ptr, int BH, int N, int D, int ks
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+#ifndef SPSATTN_PACKED_EXP
+#define SPSATTN_PACKED_EXP false
+#endif
+
 template <int D, bool FP16>
 int launch_prefill_sm100(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                          const PrefillParams& prm, cudaStream_t st) {
@@ -102,13 +106,13 @@ int launch_prefill_sm100(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(prefill_sm100_kernel<D, FP16>,
+    attr_err = cudaFuncSetAttribute(prefill_sm100_kernel<D, FP16, SPSATTN_PACKED_EXP>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   });
   if (attr_err != cudaSuccess) return (int)attr_err;
   const long long blocks = (long long)prm.n_qtiles * prm.B * prm.H;
   if (blocks <= 0 || blocks > 0x7fffffffLL) return SPSATTN_ERR_TOO_LARGE;
-  prefill_sm100_kernel<D, FP16><<<(unsigned)blocks, kPrefillThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, prm);
+  prefill_sm100_kernel<D, FP16, SPSATTN_PACKED_EXP><<<(unsigned)blocks, kPrefillThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, prm);
   return (int)cudaGetLastError();
 }
 
@@ -162,6 +166,12 @@ static int launch_decode_d(const DecodeParams& prm, int nq, bool fp16, cudaStrea
 }
 
 }  // namespace
+
+#ifdef SPSATTN_TRACE
+static long long* g_trace_buffer = nullptr;
+// tuning builds only: where the prefill kernel writes its cycle stamps
+extern "C" void spsattn_debug_set_trace(long long* device_buffer) { g_trace_buffer = device_buffer; }
+#endif
 
 extern "C" {
 
@@ -243,6 +253,9 @@ int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, fl
     prm.mask = mask;
     prm.scale_log2 = scale_log2;
     prm.status = device_status;
+#ifdef SPSATTN_TRACE
+    prm.trace = g_trace_buffer;
+#endif
     if (D == 64) return fp16 ? launch_prefill_sm100<64, true>(tq, tk, tv, prm, st)
                              : launch_prefill_sm100<64, false>(tq, tk, tv, prm, st);
     return fp16 ? launch_prefill_sm100<128, true>(tq, tk, tv, prm, st)
