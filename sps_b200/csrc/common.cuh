@@ -32,18 +32,6 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
-// 2^x on a packed pair of 16-bit floats (one special-function instruction for two elements)
-template <bool FP16>
-__device__ __forceinline__ uint32_t exp2_packed(uint32_t x) {
-  uint32_t y;
-  if constexpr (FP16) {
-    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  } else {
-    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(y) : "r"(x));
-  }
-  return y;
-}
-
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -74,6 +62,18 @@ __device__ __forceinline__ void unpack2(uint32_t u, float& lo, float& hi) {
     lo = __uint_as_float(u << 16);
     hi = __uint_as_float(u & 0xffff0000u);
   }
+}
+
+// one lane of a converged warp; the others fall through.  Keeping the warp converged around
+// tcgen05 / TMA instructions lets their operands live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -188,15 +188,31 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// D[tmem] (+)= A[smem desc] * B[smem desc]; issued by one thread
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                        uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+// D[tmem] (+)= A[smem desc] * B[smem desc]; issued by one thread.  The descriptors are passed as
+// 32-bit halves: only the low half (start address) changes between K steps and tiles, so the
+// issuing thread does one 32-bit add per operand and nothing else between two MMAs.
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                        uint32_t b_hi, uint32_t idesc) {
+  if constexpr (ACCUMULATE) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.eq.u32 p, 0, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.u32 p, 0, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
+        : "memory");
+  }
 }
 
 // the mbarrier receives one arrival when every tcgen05.mma issued so far by this thread is done

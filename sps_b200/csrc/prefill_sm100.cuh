@@ -6,11 +6,15 @@
 //   warps 0-3  softmax / correction / epilogue (thread r owns query row r = TMEM lane r)
 //   warp 4     TMEM allocation, TMA producer (lane 0)
 //   warp 5     MMA issuer (lane 0)
-// Per key tile j (128 key tokens of one parity stream):
-//   S = Q K_j^T        tcgen05.mma  128x128xD, operands K-major / 128B swizzle in shared memory
+// Per key tile j (64 key tokens of one parity stream):
+//   S = Q K_j^T        tcgen05.mma  128x64xD, operands K-major / 128B swizzle in shared memory
 //   P = exp2(S*c - m*c) softmax warps: tcgen05.ld S -> registers, mask boundary tiles only,
 //                       bf16/fp16 P written to shared memory in the K-major swizzled layout
-//   O += P V_j         tcgen05.mma  128xDx128, V consumed as the MN-major B operand as loaded
+//   O += P V_j         tcgen05.mma  128xDx64, V consumed as the MN-major B operand as loaded
+// Tiles of 64 keys keep a block small (64 KB of shared memory, 128 TMEM columns, ~110
+// registers at head_dim 64) so that three blocks share an SM: the kernel is limited by the
+// special-function unit (one exp2 per score, 16 per clock per SM) and three independent blocks
+// in different phases keep that unit busier than two larger ones.
 // Reference computation: src/modeling/models/attention/triton_sps_flash_attention.py:26-139,
 // :147-269 (and the reverse / standard variants); unlike it, tiles whose keys are all hidden
 // by the document / window / parity rule are never loaded or multiplied.
@@ -51,26 +55,28 @@ constexpr int kTraceTiles = 40;
 #endif
 
 constexpr int kTileM = 128;      // query rows per block
-constexpr int kTileN = 128;      // key tokens per tile
+constexpr int kTileN = 64;       // key tokens per tile
 constexpr int kPrefillThreads = 192;
 
 template <int D>
 struct PrefillCfg {
   static constexpr int kStagesK = 2;
-  static constexpr int kStagesV = (D == 64) ? 1 : 2;
-  static constexpr int kSBufs = (D == 64) ? 1 : 2;           // S accumulators in TMEM
-  static constexpr uint32_t kTmemCols = (D == 64) ? 256 : 512;
-  static constexpr uint32_t kColO = kSBufs * 128;             // O accumulator column offset
-  static constexpr int kTileBytes = kTileN * D * 2;           // one Q / K / V tile
-  static constexpr int kSubTileBytes = kTileN * 128;          // 128 rows x 64 elements
+  static constexpr int kStagesV = (D == 64) ? 2 : 1;
+  static constexpr int kSBufs = (D == 64) ? 1 : 2;            // S accumulators in TMEM
+  static constexpr uint32_t kTmemCols = (D == 64) ? 128 : 256;
+  static constexpr uint32_t kColO = kSBufs * kTileN;           // O accumulator column offset
+  static constexpr int kQBytes = kTileM * D * 2;               // the Q tile
+  static constexpr int kQSubBytes = kTileM * 128;              // 128 rows x 64 elements
+  static constexpr int kKVBytes = kTileN * D * 2;              // one K or V tile
+  static constexpr int kKVSubBytes = kTileN * 128;             // 64 rows x 64 elements
   static constexpr int kPBytes = kTileM * kTileN * 2;
   static constexpr int kOffQ = 0;
-  static constexpr int kOffK = kOffQ + kTileBytes;
-  static constexpr int kOffV = kOffK + kStagesK * kTileBytes;
-  static constexpr int kOffP = kOffV + kStagesV * kTileBytes;
+  static constexpr int kOffK = kOffQ + kQBytes;
+  static constexpr int kOffV = kOffK + kStagesK * kKVBytes;
+  static constexpr int kOffP = kOffV + kStagesV * kKVBytes;
   static constexpr int kOffBar = kOffP + kPBytes;
-  static constexpr int kSmemBytes = kOffBar + 256 + 1024;     // barriers + alignment slack
-  static constexpr int kBlocksPerSM = (D == 64) ? 2 : 1;
+  static constexpr int kSmemBytes = kOffBar + 256 + 1024;      // barriers + alignment slack
+  static constexpr int kBlocksPerSM = (D == 64) ? 3 : 2;
 };
 
 struct TileInfo {
@@ -101,9 +107,17 @@ __device__ __forceinline__ TileInfo tile_info(const BlockPlan& bp, int j) {
   return t;
 }
 
+// bounded wait executed by a whole converged warp; the outcome is made warp-uniform so that a
+// failure takes all 32 lanes out of their loop together
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, status);
+  return __all_sync(0xffffffffu, ok);
+}
+
 constexpr float kRescaleLog2 = 8.0f;
 
-template <int D, bool FP16, bool PACKED_EXP>
+template <int D, bool FP16>
 __global__ void __launch_bounds__(kPrefillThreads, PrefillCfg<D>::kBlocksPerSM)
 prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const PrefillParams prm) {
@@ -188,9 +202,9 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       fence_barrier_init();
       // the Q tile depends on nothing but the block index: start it before the plan is known
       tma_prefetch_desc(&tm_q);
-      mbar_arrive_expect_tx(bar_q_full, Cfg::kTileBytes);
+      mbar_arrive_expect_tx(bar_q_full, Cfg::kQBytes);
       for (int c = 0; c < D / 64; ++c)
-        tma_load_3d(sQ + c * Cfg::kSubTileBytes, &tm_q, bar_q_full, c * 64, i0, bh);
+        tma_load_3d(sQ + c * Cfg::kQSubBytes, &tm_q, bar_q_full, c * 64, i0, bh);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
     }
@@ -211,33 +225,40 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (!bail && n_tiles > 0) {
     if (warp == 4) {
       // ------------------------------------------------------------------ TMA producer
-      if (lane == 0) {
+      // converged warp, one elected lane issues the copies (tensor-map operands stay uniform)
+      {
         auto load_k = [&](int j) {
           const TileInfo t = tile_info(s_plan, j);
           const int st = j % Cfg::kStagesK;
           if (j >= Cfg::kStagesK) {
-            if (!mbar_wait(bar_k_empty + 8 * st, ((j / Cfg::kStagesK) - 1) & 1, abort_flag, prm.status))
+            if (!warp_wait(bar_k_empty + 8 * st, ((j / Cfg::kStagesK) - 1) & 1, abort_flag, prm.status))
               return false;
           }
-          mbar_arrive_expect_tx(bar_k_full + 8 * st, Cfg::kTileBytes);
-          for (int c = 0; c < D / 64; ++c)
-            tma_load_4d(sK + st * Cfg::kTileBytes + c * Cfg::kSubTileBytes, &tm_k, bar_k_full + 8 * st,
-                        c * 64, t.stream, t.k0, bh);
-          SPS_TRACE(j, 13);
+          if (elect_one()) {
+            mbar_arrive_expect_tx(bar_k_full + 8 * st, Cfg::kKVBytes);
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_4d(sK + st * Cfg::kKVBytes + c * Cfg::kKVSubBytes, &tm_k, bar_k_full + 8 * st,
+                          c * 64, t.stream, t.k0, bh);
+          }
+          __syncwarp();
+          if (lane == 0) SPS_TRACE(j, 13);
           return true;
         };
         auto load_v = [&](int j) {
           const TileInfo t = tile_info(s_plan, j);
           const int st = j % Cfg::kStagesV;
           if (j >= Cfg::kStagesV) {
-            if (!mbar_wait(bar_v_empty + 8 * st, ((j / Cfg::kStagesV) - 1) & 1, abort_flag, prm.status))
+            if (!warp_wait(bar_v_empty + 8 * st, ((j / Cfg::kStagesV) - 1) & 1, abort_flag, prm.status))
               return false;
           }
-          mbar_arrive_expect_tx(bar_v_full + 8 * st, Cfg::kTileBytes);
-          for (int c = 0; c < D / 64; ++c)
-            tma_load_4d(sV + st * Cfg::kTileBytes + c * Cfg::kSubTileBytes, &tm_v, bar_v_full + 8 * st,
-                        c * 64, t.stream, t.k0, bh);
-          SPS_TRACE(j, 14);
+          if (elect_one()) {
+            mbar_arrive_expect_tx(bar_v_full + 8 * st, Cfg::kKVBytes);
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_4d(sV + st * Cfg::kKVBytes + c * Cfg::kKVSubBytes, &tm_v, bar_v_full + 8 * st,
+                          c * 64, t.stream, t.k0, bh);
+          }
+          __syncwarp();
+          if (lane == 0) SPS_TRACE(j, 14);
           return true;
         };
         bool ok = load_k(0);
@@ -246,63 +267,80 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           if (ok) ok = load_v(j);
         }
       }
-      __syncwarp();
     } else if (warp == 5) {
       // ------------------------------------------------------------------ MMA issuer
-      if (lane == 0) {
+      // The whole warp runs this loop converged (so descriptors and addresses stay in uniform
+      // registers); one elected lane issues the tcgen05 instructions.
+      {
         constexpr uint32_t idesc_qk = make_idesc_f16(FP16, kTileM, kTileN, false, false);
         constexpr uint32_t idesc_pv = make_idesc_f16(FP16, kTileM, D, false, true);
-        // descriptors differ from tile to tile only in the start-address field (low 14 bits)
-        const uint64_t desc_q0 = make_smem_desc_sw128(sQ, 16, 1024);
-        const uint64_t desc_k0 = make_smem_desc_sw128(sK, 16, 1024);
-        const uint64_t desc_p0 = make_smem_desc_sw128(sP, 16, 1024);
-        const uint64_t desc_v0 = make_smem_desc_sw128(sV, Cfg::kSubTileBytes, 1024);
+        // descriptors differ from tile to tile and K step to K step only in the start-address
+        // field, which lives in the low 32 bits
+        const uint64_t dq64 = make_smem_desc_sw128(sQ, 16, 1024);
+        const uint64_t dk64 = make_smem_desc_sw128(sK, 16, 1024);
+        const uint64_t dp64 = make_smem_desc_sw128(sP, 16, 1024);
+        const uint64_t dv64 = make_smem_desc_sw128(sV, Cfg::kKVSubBytes, 1024);
+        const uint32_t dq_lo = (uint32_t)dq64, dq_hi = (uint32_t)(dq64 >> 32);
+        const uint32_t dk_lo = (uint32_t)dk64, dk_hi = (uint32_t)(dk64 >> 32);
+        const uint32_t dp_lo = (uint32_t)dp64, dp_hi = (uint32_t)(dp64 >> 32);
+        const uint32_t dv_lo = (uint32_t)dv64, dv_hi = (uint32_t)(dv64 >> 32);
         auto issue_qk = [&](int j) {
           const int st = j % Cfg::kStagesK;
           const int sb = j % Cfg::kSBufs;
-          if (!mbar_wait(bar_k_full + 8 * st, (j / Cfg::kStagesK) & 1, abort_flag, prm.status)) return false;
+          if (!warp_wait(bar_k_full + 8 * st, (j / Cfg::kStagesK) & 1, abort_flag, prm.status)) return false;
           if (j >= Cfg::kSBufs) {
-            if (!mbar_wait(bar_s_free + 8 * sb, ((j / Cfg::kSBufs) - 1) & 1, abort_flag, prm.status))
+            if (!warp_wait(bar_s_free + 8 * sb, ((j / Cfg::kSBufs) - 1) & 1, abort_flag, prm.status))
               return false;
           }
           tc_fence_after();
-          const uint64_t db0 = desc_k0 + (uint64_t)((st * Cfg::kTileBytes) >> 4);
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t kb0 = dk_lo + ((st * Cfg::kKVBytes) >> 4);
+          const uint32_t sd = tmem + sb * kTileN;
+          if (elect_one()) {
             // a K step of 16 elements is 32 bytes inside a 128-byte row; 64 elements per sub-tile
-            const uint64_t off = (uint64_t)(((kk / 4) * Cfg::kSubTileBytes + (kk % 4) * 32) >> 4);
-            umma_ss(tmem + sb * 128, desc_q0 + off, db0 + off, idesc_qk, kk > 0 ? 1u : 0u);
+            umma_ss<false>(sd, dq_lo, dq_hi, kb0, dk_hi, idesc_qk);
+#pragma unroll
+            for (int kk = 1; kk < D / 16; ++kk) {
+              const uint32_t qa = ((kk / 4) * Cfg::kQSubBytes + (kk % 4) * 32) >> 4;
+              const uint32_t kb = ((kk / 4) * Cfg::kKVSubBytes + (kk % 4) * 32) >> 4;
+              umma_ss<true>(sd, dq_lo + qa, dq_hi, kb0 + kb, dk_hi, idesc_qk);
+            }
+            umma_commit(bar_s_full + 8 * sb);
+            umma_commit(bar_k_empty + 8 * st);
           }
-          umma_commit(bar_s_full + 8 * sb);
-          umma_commit(bar_k_empty + 8 * st);
-          SPS_TRACE(j, 9);
+          __syncwarp();
+          if (lane == 0) SPS_TRACE(j, 9);
           return true;
         };
-        bool ok = mbar_wait(bar_q_full, 0, abort_flag, prm.status);
+        bool ok = warp_wait(bar_q_full, 0, abort_flag, prm.status);
         if (ok) ok = issue_qk(0);
         for (int j = 0; ok && j < n_tiles; ++j) {
           if (j + 1 < n_tiles) ok = issue_qk(j + 1);
           if (!ok) break;
           const int st = j % Cfg::kStagesV;
-          if (!mbar_wait(bar_p_full, j & 1, abort_flag, prm.status)) break;
-          SPS_TRACE(j, 10);
-          if (!mbar_wait(bar_v_full + 8 * st, (j / Cfg::kStagesV) & 1, abort_flag, prm.status)) break;
-          SPS_TRACE(j, 11);
+          if (!warp_wait(bar_p_full, j & 1, abort_flag, prm.status)) break;
+          if (lane == 0) SPS_TRACE(j, 10);
+          if (!warp_wait(bar_v_full + 8 * st, (j / Cfg::kStagesV) & 1, abort_flag, prm.status)) break;
+          if (lane == 0) SPS_TRACE(j, 11);
           tc_fence_after();
-          const uint64_t dv0 = desc_v0 + (uint64_t)((st * Cfg::kTileBytes) >> 4);
+          const uint32_t vb0 = dv_lo + ((st * Cfg::kKVBytes) >> 4);
+          const uint32_t od = tmem + Cfg::kColO;
+          if (elect_one()) {
+            // P: K-major, one 64-key sub-tile; V: MN-major, 16 key rows = 2048 bytes per step
+            if (j > 0) {
+              umma_ss<true>(od, dp_lo, dp_hi, vb0, dv_hi, idesc_pv);
+            } else {
+              umma_ss<false>(od, dp_lo, dp_hi, vb0, dv_hi, idesc_pv);
+            }
 #pragma unroll
-          for (int kk = 0; kk < kTileN / 16; ++kk) {
-            // P: K-major, two 64-key sub-tiles; V: MN-major, 16 key rows = 2048 bytes per step
-            const uint64_t pa = (uint64_t)(((kk / 4) * (kTileM * 128) + (kk % 4) * 32) >> 4);
-            umma_ss(tmem + Cfg::kColO, desc_p0 + pa, dv0 + (uint64_t)((kk * 2048) >> 4), idesc_pv,
-                    (j > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 1; kk < kTileN / 16; ++kk)
+              umma_ss<true>(od, dp_lo + ((kk * 32) >> 4), dp_hi, vb0 + ((kk * 2048) >> 4), dv_hi, idesc_pv);
+            umma_commit(bar_pv_done);
+            umma_commit(bar_v_empty + 8 * st);
           }
-          umma_commit(bar_pv_done);
-          umma_commit(bar_v_empty + 8 * st);
-          SPS_TRACE(j, 12);
+          __syncwarp();
+          if (lane == 0) SPS_TRACE(j, 12);
         }
       }
-      __syncwarp();
     } else {
       // ------------------------------------------------------------------ softmax warps
       const int row = tid;                 // TMEM lane and query row inside the tile
@@ -343,18 +381,14 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tc_fence_after();
         float s[kTileN];
         {
-          uint32_t r0[32], r1[32], r2[32], r3[32];
-          tmem_ld32(tmem + lane_addr + sb * 128, r0);
-          tmem_ld32(tmem + lane_addr + sb * 128 + 32, r1);
-          tmem_ld32(tmem + lane_addr + sb * 128 + 64, r2);
-          tmem_ld32(tmem + lane_addr + sb * 128 + 96, r3);
+          uint32_t r0[32], r1[32];
+          tmem_ld32(tmem + lane_addr + sb * kTileN, r0);
+          tmem_ld32(tmem + lane_addr + sb * kTileN + 32, r1);
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             s[e] = __uint_as_float(r0[e]);
             s[32 + e] = __uint_as_float(r1[e]);
-            s[64 + e] = __uint_as_float(r2[e]);
-            s[96 + e] = __uint_as_float(r3[e]);
           }
         }
         tc_fence_before();
@@ -369,9 +403,9 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (e < cmin || e > cmax) s[e] = -INFINITY;
           if (general) {
             // ids are not monotone: compare this row's id with each key's id (uniform loads)
-            uint32_t same[4];
+            uint32_t same[kTileN / 32];
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
+            for (int q4 = 0; q4 < kTileN / 32; ++q4) {
               uint32_t bits = 0;
               for (int e = 0; e < 32; ++e) {
                 const int jrow = prm.mask.ks * (t.k0 + q4 * 32 + e) + t.stream;
@@ -422,19 +456,10 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         uint32_t pk[kTileN / 2];
 #pragma unroll
         for (int e = 0; e < kTileN; e += 2) {
-          if constexpr (PACKED_EXP) {
-            const uint32_t xp = pack2<FP16>(fmaf(s[e], c, neg_mc), fmaf(s[e + 1], c, neg_mc));
-            const uint32_t pp = exp2_packed<FP16>(xp);
-            float p0, p1;
-            unpack2<FP16>(pp, p0, p1);
-            sum4[(e / 2) & 3] += p0 + p1;
-            pk[e / 2] = pp;
-          } else {
-            const float p0 = fast_exp2(fmaf(s[e], c, neg_mc));
-            const float p1 = fast_exp2(fmaf(s[e + 1], c, neg_mc));
-            sum4[(e / 2) & 3] += p0 + p1;
-            pk[e / 2] = pack2<FP16>(p0, p1);
-          }
+          const float p0 = fast_exp2(fmaf(s[e], c, neg_mc));
+          const float p1 = fast_exp2(fmaf(s[e + 1], c, neg_mc));
+          sum4[(e / 2) & 3] += p0 + p1;
+          pk[e / 2] = pack2<FP16>(p0, p1);
         }
         l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         if (tid == 0) SPS_TRACE(j, 4);
@@ -448,17 +473,13 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         if (tid == 0) SPS_TRACE(j, 5);
         // P -> shared memory, K-major 128B-swizzled: 16-byte chunk ch of row r sits at
-        // r * 128 + ((ch ^ (r & 7)) << 4) inside each [128 x 64] sub-tile
+        // r * 128 + ((ch ^ (r & 7)) << 4) of the [128 x 64] tile
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-#pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
-            const uint32_t addr = sP + sub * (kTileM * 128) + row * 128 + ((ch ^ (row & 7)) << 4);
-            const int e = sub * 32 + ch * 4;
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[e]),
-                         "r"(pk[e + 1]), "r"(pk[e + 2]), "r"(pk[e + 3])
-                         : "memory");
-          }
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint32_t addr = sP + row * 128 + ((ch ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[ch * 4]),
+                       "r"(pk[ch * 4 + 1]), "r"(pk[ch * 4 + 2]), "r"(pk[ch * 4 + 3])
+                       : "memory");
         }
         if (tid == 0) SPS_TRACE(j, 6);
         if (j > 0 && rescale) {

@@ -77,15 +77,15 @@ int encode_q_map(CUtensorMap* tm, const void* ptr, int BH, int N, int D, int dty
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
-// K / V map with the two parity streams as a dimension: [D, ks, N/ks, BH], box [64, 1, 128, 1].
-// A tile is 128 consecutive key tokens of one parity; rows of the other parity are skipped by
+// K / V map with the two parity streams as a dimension: [D, ks, N/ks, BH], box [64, 1, kTileN, 1].
+// A tile is kTileN consecutive key tokens of one parity; rows of the other parity are skipped by
 // the stride, out-of-range tokens read as zero and the next head is never touched.
 int encode_kv_map(CUtensorMap* tm, const void* ptr, int BH, int N, int D, int ks, int dtype) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return SPSATTN_ERR_DRIVER;
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)ks, (cuuint64_t)(N / ks), (cuuint64_t)BH};
   cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)ks * D * 2, (cuuint64_t)N * D * 2};
-  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)kTileN, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(tm, dtype == SPSATTN_DTYPE_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
@@ -95,10 +95,6 @@ int encode_kv_map(CUtensorMap* tm, const void* ptr, int BH, int N, int D, int ks
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
-#ifndef SPSATTN_PACKED_EXP
-#define SPSATTN_PACKED_EXP false
-#endif
-
 template <int D, bool FP16>
 int launch_prefill_sm100(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                          const PrefillParams& prm, cudaStream_t st) {
@@ -106,13 +102,13 @@ int launch_prefill_sm100(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(prefill_sm100_kernel<D, FP16, SPSATTN_PACKED_EXP>,
+    attr_err = cudaFuncSetAttribute(prefill_sm100_kernel<D, FP16>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   });
   if (attr_err != cudaSuccess) return (int)attr_err;
   const long long blocks = (long long)prm.n_qtiles * prm.B * prm.H;
   if (blocks <= 0 || blocks > 0x7fffffffLL) return SPSATTN_ERR_TOO_LARGE;
-  prefill_sm100_kernel<D, FP16, SPSATTN_PACKED_EXP><<<(unsigned)blocks, kPrefillThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, prm);
+  prefill_sm100_kernel<D, FP16><<<(unsigned)blocks, kPrefillThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, prm);
   return (int)cudaGetLastError();
 }
 
