@@ -33,6 +33,7 @@ if ROOT not in sys.path:
 
 PREFILL = "cfg1_s_scale"
 DECODE = "cfg2_segmented_decode"
+PREFILL_FULL_WINDOW = "cfg4_full_window"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -218,9 +219,33 @@ def run_ours(args):
         }
         del hq, hk, hv, ho, dq, dk, dv
 
+    # ---------------- the least sparse prefill mask: head_dim 128, window = whole document
+    if not args.skip_full_window:
+        del wl, out
+        torch.cuda.empty_cache()
+        wf = workloads.make_prefill(PREFILL_FULL_WINDOW, device, seed=rank)
+        outf = torch.empty_like(wf.q)
+
+        def full_window_step():
+            sps_b200.prefill_attention(wf.q, wf.k, wf.v, wf.sm_scale, persistent_parity=0,
+                                       temporary_window=wf.window, documents_idx=None, out=outf)
+
+        kf = max(3, min(K, 30))
+        f_region, f_launch = timed_steps(full_window_step, kf, 3, world, device)
+        tf = wf.flops / (f_launch * 1e-3) / 1e12
+        result["prefill_full_window"] = {
+            "workload": f"{PREFILL_FULL_WINDOW}: [B=4,H=16,2T=8192,D=128] bf16, w=4096, one document per row, per GPU",
+            "useful_gflop_per_step_per_gpu": wf.flops / 1e9, "ms_per_step": f_region / kf,
+            "useful_tflops": world * wf.flops * kf / (f_region * 1e-3) / 1e12, "gpu_launches": kf,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                         "traffic": None, "peak_source": f"{peak_kind} bf16 burst", "launch_ms": f_launch},
+        }
+        wl = out = None
+        del wf, outf
+
     # ---------------- segmented decode step (second half of the metric)
     if not args.skip_decode:
-        del wl, out
+        wl = out = None
         torch.cuda.empty_cache()
         dw = workloads.make_decode(DECODE, device, seed=rank)
         segs = [sps_b200.KVSegment(dw.ring_k, dw.ring_v, dw.ring_len, max_len_cap=dw.ring_k.shape[2]),
@@ -370,6 +395,7 @@ def main():
     ap.add_argument("--case", choices=["full", "prefill-small", "decode-small"], default="full")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--skip-full-window", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

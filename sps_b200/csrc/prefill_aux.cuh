@@ -14,9 +14,11 @@ __device__ __forceinline__ long long load_doc(const void* docs, int is_i64, size
 
 // One block per batch row: lo[b][i] = first row of the run of equal ids containing row i
 // (inclusive max-scan of run-start positions), mono[b] = 1 iff the ids never decrease.
+// Each thread scans kItems consecutive rows, so rows up to 8192 need a single pass.
 __global__ void __launch_bounds__(1024)
 doc_prepass_kernel(const void* docs, int is_i64, int64_t stride_b, int64_t stride_t, int N,
                    int* __restrict__ lo, int* __restrict__ mono) {
+  constexpr int kItems = 8;
   __shared__ int s_warp[32];
   __shared__ int s_carry;
   __shared__ int s_mono;
@@ -30,24 +32,33 @@ doc_prepass_kernel(const void* docs, int is_i64, int64_t stride_b, int64_t strid
     s_mono = 1;
   }
   __syncthreads();
-  for (int c0 = 0; c0 < N; c0 += 1024) {
-    const int i = c0 + tid;
-    int start = 0;
-    bool dec = false;
-    if (i < N && i > 0) {
-      const long long d = load_doc(base, is_i64, (size_t)i * stride_t);
-      const long long dp = load_doc(base, is_i64, (size_t)(i - 1) * stride_t);
-      start = (d != dp) ? i : 0;
-      dec = d < dp;
+  bool dec = false;
+  for (int c0 = 0; c0 < N; c0 += 1024 * kItems) {
+    const int i0 = c0 + tid * kItems;
+    int v[kItems];
+    long long prev = 0;
+    if (i0 > 0 && i0 - 1 < N) prev = load_doc(base, is_i64, (size_t)(i0 - 1) * stride_t);
+    int run = 0;
+#pragma unroll
+    for (int x = 0; x < kItems; ++x) {
+      const int i = i0 + x;
+      if (i < N) {
+        const long long d = load_doc(base, is_i64, (size_t)i * stride_t);
+        if (i > 0) {
+          if (d != prev) run = i;
+          dec |= d < prev;
+        }
+        prev = d;
+      }
+      v[x] = run;   // inclusive max of the run starts inside this thread's span
     }
-    if (dec) s_mono = 0;
-    int v = start;
+    int tot = run;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int u = __shfl_up_sync(0xffffffffu, v, o);
-      if (lane >= o) v = max(v, u);
+      const int u = __shfl_up_sync(0xffffffffu, tot, o);
+      if (lane >= o) tot = max(tot, u);
     }
-    if (lane == 31) s_warp[warp] = v;
+    if (lane == 31) s_warp[warp] = tot;
     __syncthreads();
     if (warp == 0) {
       int wv = s_warp[lane];
@@ -59,14 +70,18 @@ doc_prepass_kernel(const void* docs, int is_i64, int64_t stride_b, int64_t strid
       s_warp[lane] = wv;
     }
     __syncthreads();
-    const int carry = s_carry;
-    const int prev = warp > 0 ? s_warp[warp - 1] : 0;
-    v = max(max(v, prev), carry);
-    if (i < N) lo[(size_t)b * N + i] = v;
+    int pre = __shfl_up_sync(0xffffffffu, tot, 1);   // everything before this thread in its warp
+    if (lane == 0) pre = 0;
+    pre = max(pre, max(s_carry, warp > 0 ? s_warp[warp - 1] : 0));
+#pragma unroll
+    for (int x = 0; x < kItems; ++x)
+      if (i0 + x < N) lo[(size_t)b * N + i0 + x] = max(v[x], pre);
     __syncthreads();
-    if (tid == 1023) s_carry = v;
+    if (tid == 1023) s_carry = max(tot, pre);
     __syncthreads();
   }
+  if (dec) s_mono = 0;
+  __syncthreads();
   if (tid == 0) mono[b] = s_mono;
 }
 
