@@ -34,6 +34,10 @@ if ROOT not in sys.path:
 PREFILL = "cfg1_s_scale"
 DECODE = "cfg2_segmented_decode"
 PREFILL_FULL_WINDOW = "cfg4_full_window"
+# DRAM traffic per full-size launch, from ncu captures of a smaller case scaled by the units
+# processed (traffic is proportional to batch rows / sequences)
+PREFILL_DRAM_BYTES_PER_LAUNCH = 2 * (151.4e6 + 34.0e6)
+DECODE_DRAM_BYTES_PER_LAUNCH = 4 * (323.7e6 + 6.4e6)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -188,7 +192,8 @@ def run_ours(args):
         "gpu_launches": 2 * K,      # document pre-pass + attention kernel per step
         "roofline": {
             "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-            "frac": achieved / peak, "traffic": None,
+            "frac": achieved / peak, "traffic": PREFILL_DRAM_BYTES_PER_LAUNCH,
+            "traffic_source": "ncu dram__bytes_read+write of a 4-row launch x2 (profiles/prefill_sm100_d64_cfg1_half_batch.md)",
             "peak_source": f"{peak_kind} bf16 burst (kernel timed alone)",
             "launch_ms": launch_ms,
         },
@@ -267,7 +272,10 @@ def run_ours(args):
             "tokens_per_s": world * S * K / (d_region * 1e-3), "ms_per_step": d_region / K,
             "algorithmic_mb_per_step": dw.bytes / 1e6, "gpu_launches": 2 * K,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
-                         "traffic": None, "peak_source": f"{peak_kind} copy bandwidth", "launch_ms": d_launch},
+                         "traffic": DECODE_DRAM_BYTES_PER_LAUNCH,
+                         "traffic_source": "ncu dram__bytes_read+write of a 32-sequence launch x4 "
+                                           "(profiles/decode_split_d64_cfg2_32seq.md)",
+                         "peak_source": f"{peak_kind} copy bandwidth", "launch_ms": d_launch},
         }
         sps_b200.check_device_status(device)
 
