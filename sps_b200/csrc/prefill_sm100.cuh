@@ -77,6 +77,7 @@ struct PrefillCfg {
   static constexpr int kOffBar = kOffP + kPBytes;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;      // barriers + alignment slack
   static constexpr int kBlocksPerSM = (D == 64) ? 3 : 2;
+  static constexpr bool kIncrementalWalk = (D != 64);
 };
 
 struct TileInfo {
@@ -369,8 +370,33 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const float c = prm.scale_log2;
       bool ok = true;
 
+      // With registers to spare (head_dim 128: 2 blocks/SM) the tile sequence is walked
+      // incrementally — stream 0 from its top tile downwards, then stream 1 — instead of being
+      // recomputed from the plan for every tile; at head_dim 64 the 96-register budget of three
+      // blocks per SM makes the extra live values cost more in spills than they save.
+      const int n_tiles0 = s_plan.sp[0].ntiles;
+      int cur = 0;
+      int k0 = s_plan.sp[0].top - (kTileN - 1) + kTileN;
+      int kmin_hi = s_plan.sp[0].kmin_hi, kmax_lo = s_plan.sp[0].kmax_lo;
+      bool always_mask = s_plan.sp[0].force_mask || general;
+
       for (int j = 0; j < n_tiles; ++j) {
-        const TileInfo t = tile_info(s_plan, j);
+        TileInfo t;
+        if constexpr (Cfg::kIncrementalWalk) {
+          if (j == n_tiles0) {
+            cur = 1;
+            k0 = s_plan.sp[1].top - (kTileN - 1) + kTileN;
+            kmin_hi = s_plan.sp[1].kmin_hi;
+            kmax_lo = s_plan.sp[1].kmax_lo;
+            always_mask = s_plan.sp[1].force_mask || general;
+          }
+          k0 -= kTileN;
+          t.stream = s_plan.stream_id[cur];
+          t.k0 = k0;
+          t.masked = always_mask || !(kmin_hi <= k0 && kmax_lo >= k0 + kTileN - 1);
+        } else {
+          t = tile_info(s_plan, j);
+        }
         const int sb = j % Cfg::kSBufs;
         if (tid == 0) SPS_TRACE(j, 0);
         if (!mbar_wait(bar_s_full + 8 * sb, (j / Cfg::kSBufs) & 1, abort_flag, prm.status)) {
