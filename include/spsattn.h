@@ -86,6 +86,25 @@ int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, fl
                         void* workspace, size_t workspace_bytes,
                         int* device_status, void* stream);
 
+/* Same computation on operands that are not dense [B, H, N, D] blocks: element (b, h, n, d) of an
+ * operand lives at  strides[0]*b + strides[1]*h + strides[2]*n + d  (elements; d contiguous, every
+ * stride a multiple of 8 and >= D).  The reference's model code hands its kernels transposed views
+ * of token-major [B, N, H, D] projections (src/modeling/models/sps/core.py:45-55) and transposes
+ * the result back (:79); with strides the kernel reads and writes those layouts in place — q, k, v
+ * even straight out of a fused [B, N, 3*H*D] projection buffer — so the .contiguous() copies of
+ * triton_sps_flash_attention.py:504-506 disappear.  D in {64, 128}; the other head dims need dense
+ * operands. */
+int spsattn_prefill_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse,
+                                const int64_t* q_strides, const int64_t* k_strides,
+                                const int64_t* v_strides, const int64_t* o_strides,
+                                const void* doc_ids, int doc_is_i64, int64_t doc_stride_b,
+                                int64_t doc_stride_t,
+                                int B, int H, int N, int D, int dtype, float sm_scale,
+                                int persistent_parity, int temporary_window, int persistent_window,
+                                int mask_flags,
+                                void* workspace, size_t workspace_bytes,
+                                int* device_status, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Decode: nq (1 or 2) queries per (sequence, head) over up to 3 length-masked KV segments plus up
  * to 2 single-token "current" K/V entries; fp32 output [S, nq, H, D].

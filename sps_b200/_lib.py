@@ -20,7 +20,7 @@ FLAG_PERSISTENT_Q_SKIPS_TEMPORARY = 1
 
 EXPORTS = (
     "spsattn_version", "spsattn_strerror",
-    "spsattn_prefill_workspace_bytes", "spsattn_prefill_fwd",
+    "spsattn_prefill_workspace_bytes", "spsattn_prefill_fwd", "spsattn_prefill_fwd_strided",
     "spsattn_decode_workspace_bytes", "spsattn_decode_fwd", "spsattn_decode_fwd_noalloc",
     "spsattn_kv_update", "spsattn_debug_visibility",
 )
@@ -68,6 +68,10 @@ def load() -> C.CDLL:
     lib.spsattn_prefill_fwd.restype = i32
     lib.spsattn_prefill_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i64, i32, i32, i32, i32, i32,
                                         f32, i32, i32, i32, i32, vp, sz, vp, vp]
+    p64 = C.POINTER(C.c_int64)
+    lib.spsattn_prefill_fwd_strided.restype = i32
+    lib.spsattn_prefill_fwd_strided.argtypes = [vp, vp, vp, vp, vp, p64, p64, p64, p64, vp, i32, i64, i64,
+                                                i32, i32, i32, i32, i32, f32, i32, i32, i32, i32, vp, sz, vp, vp]
     lib.spsattn_decode_workspace_bytes.restype = sz
     lib.spsattn_decode_workspace_bytes.argtypes = [i32, i32, i32, i32, C.POINTER(Segment), i32]
     lib.spsattn_decode_fwd.restype = i32

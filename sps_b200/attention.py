@@ -10,6 +10,7 @@ All compute happens in libspsattn.so (tcgen05 / TMA kernel for head_dim 64 and 1
 
 from __future__ import annotations
 
+import ctypes as C
 from typing import Optional
 
 import torch
@@ -46,6 +47,13 @@ def _dtype_code(t: torch.Tensor) -> int:
     raise TypeError(f"sps_b200 attention computes in bf16 or fp16, got {t.dtype}")
 
 
+def _addressable(t: torch.Tensor) -> bool:
+    """Rows of D contiguous elements, 16-byte aligned, batch/head/token strides multiples of 8."""
+    D = t.shape[-1]
+    return (t.stride(3) == 1 and t.data_ptr() % 16 == 0 and
+            all(s % 8 == 0 and s >= D for s in t.stride()[:3]))
+
+
 def _forward_only(*tensors) -> None:
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
         raise RuntimeError(
@@ -76,7 +84,6 @@ def prefill_attention(
     if not q.is_cuda:
         raise RuntimeError("sps_b200 attention needs CUDA tensors; there is no CPU path")
     _forward_only(q, k, v)
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     B, H, N, D = q.shape
     assert k.shape == q.shape and v.shape == q.shape, "q, k, v must have the same shape"
     assert k.dtype == q.dtype and v.dtype == q.dtype, "q, k, v must have the same dtype"
@@ -84,6 +91,12 @@ def prefill_attention(
     if persistent_parity != _lib.PARITY_NONE:
         assert N % 2 == 0, "Expected doubled sequence length (2T)."
     dt = _dtype_code(q)
+    # The tensor-core kernel reads any layout whose rows are contiguous (for instance the
+    # transposed views of token-major projections the reference's modules pass); only what it
+    # cannot address is copied, where the reference copies always
+    # (triton_sps_flash_attention.py:504-506).
+    strided_ok = D in (64, 128)
+    q, k, v = (x if (strided_ok and _addressable(x)) else x.contiguous() for x in (q, k, v))
     docs_ptr, docs_i64, sb, st = None, 0, 0, 0
     if documents_idx is not None:
         docs = documents_idx
@@ -93,15 +106,23 @@ def prefill_attention(
             docs = docs.to(torch.int64)
         docs_ptr, docs_i64 = docs.data_ptr(), int(docs.dtype == torch.int64)
         sb, st = docs.stride()
-    o = torch.empty_like(q) if out is None else out
+    if out is not None:
+        o = out
+    elif strided_ok and q.stride(2) > q.stride(1):
+        # token-major input: produce token-major output, so that the caller's
+        # y.transpose(1, 2).contiguous() (sps/core.py:79) is free
+        o = torch.empty((B, N, H, D), dtype=q.dtype, device=q.device).transpose(1, 2)
+    else:
+        o = torch.empty((B, H, N, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device) if return_lse else None
     ws_bytes = lib.spsattn_prefill_workspace_bytes(B, H, N, D) if documents_idx is not None else 0
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
     pw = _lib.NO_WINDOW if persistent_window is None else max(-1, min(int(persistent_window), N))
+    arr = lambda t: (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
     with torch.cuda.device(q.device):
-        rc = lib.spsattn_prefill_fwd(
+        rc = lib.spsattn_prefill_fwd_strided(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-            None if lse is None else lse.data_ptr(),
+            None if lse is None else lse.data_ptr(), arr(q), arr(k), arr(v), arr(o),
             docs_ptr, docs_i64, sb, st, B, H, N, D, dt, float(sm_scale), int(persistent_parity),
             max(-1, min(int(temporary_window), N)), pw, int(mask_flags),
             None if ws is None else ws.data_ptr(), ws_bytes,

@@ -26,7 +26,8 @@
 namespace spsattn {
 
 struct PrefillParams {
-  void* o;               // [B,H,N,D]
+  void* o;               // rows of D contiguous elements, addressed with the strides below
+  int64_t o_stride_b, o_stride_h, o_stride_n;   // elements
   float* lse;            // [B,H,N] or null
   const void* docs;      // [B,N] ids or null
   int64_t doc_stride_b, doc_stride_t;
@@ -137,6 +138,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int bh = blockIdx.x / prm.n_qtiles;
   const int qt = prm.n_qtiles - 1 - (blockIdx.x % prm.n_qtiles);
   const int b = bh / prm.H;
+  const int h = bh - b * prm.H;
   const int i0 = qt * kTileM;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -205,7 +207,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tma_prefetch_desc(&tm_q);
       mbar_arrive_expect_tx(bar_q_full, Cfg::kQBytes);
       for (int c = 0; c < D / 64; ++c)
-        tma_load_3d(sQ + c * Cfg::kQSubBytes, &tm_q, bar_q_full, c * 64, i0, bh);
+        tma_load_4d(sQ + c * Cfg::kQSubBytes, &tm_q, bar_q_full, c * 64, i0, h, b);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
     }
@@ -238,8 +240,8 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           if (elect_one()) {
             mbar_arrive_expect_tx(bar_k_full + 8 * st, Cfg::kKVBytes);
             for (int c = 0; c < D / 64; ++c)
-              tma_load_4d(sK + st * Cfg::kKVBytes + c * Cfg::kKVSubBytes, &tm_k, bar_k_full + 8 * st,
-                          c * 64, t.stream, t.k0, bh);
+              tma_load_5d(sK + st * Cfg::kKVBytes + c * Cfg::kKVSubBytes, &tm_k, bar_k_full + 8 * st,
+                          c * 64, t.stream, t.k0, h, b);
           }
           __syncwarp();
           if (lane == 0) SPS_TRACE(j, 13);
@@ -255,8 +257,8 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           if (elect_one()) {
             mbar_arrive_expect_tx(bar_v_full + 8 * st, Cfg::kKVBytes);
             for (int c = 0; c < D / 64; ++c)
-              tma_load_4d(sV + st * Cfg::kKVBytes + c * Cfg::kKVSubBytes, &tm_v, bar_v_full + 8 * st,
-                          c * 64, t.stream, t.k0, bh);
+              tma_load_5d(sV + st * Cfg::kKVBytes + c * Cfg::kKVSubBytes, &tm_v, bar_v_full + 8 * st,
+                          c * 64, t.stream, t.k0, h, b);
           }
           __syncwarp();
           if (lane == 0) SPS_TRACE(j, 14);
@@ -532,7 +534,8 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (ok) {
         tc_fence_after();
         const float inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
-        uint8_t* o_row = reinterpret_cast<uint8_t*>(prm.o) + ((size_t)bh * prm.N + i) * (D * 2);
+        uint8_t* o_row = reinterpret_cast<uint8_t*>(prm.o) +
+                         (b * prm.o_stride_b + h * prm.o_stride_h + i * prm.o_stride_n) * 2;
 #pragma unroll
         for (int q4 = 0; q4 < D / 32; ++q4) {
           uint32_t r[32];
@@ -559,8 +562,9 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // nothing visible for any row of this tile: outputs are zero
     const int i = i0 + tid;
     if (i < prm.N) {
-      uint4* o_row = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(prm.o) +
-                                              ((size_t)bh * prm.N + i) * (D * 2));
+      uint4* o_row = reinterpret_cast<uint4*>(
+          reinterpret_cast<uint8_t*>(prm.o) +
+          (b * prm.o_stride_b + h * prm.o_stride_h + i * prm.o_stride_n) * 2);
       for (int e = 0; e < D / 8; ++e) o_row[e] = make_uint4(0, 0, 0, 0);
       if (prm.lse != nullptr) prm.lse[(size_t)bh * prm.N + i] = -INFINITY;
     }

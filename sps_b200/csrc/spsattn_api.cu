@@ -61,31 +61,18 @@ MaskParams make_mask(int N, int parity, int w, int pw, int flags) {
   return m;
 }
 
-// Q / O style map: [D, N, BH], box [64, 128, 1]
-int encode_q_map(CUtensorMap* tm, const void* ptr, int BH, int N, int D, int dtype) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return SPSATTN_ERR_DRIVER;
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)N * D * 2};
-  cuuint32_t box[3] = {64, 128, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(tm, dtype == SPSATTN_DTYPE_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                   3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : (int)r;
-}
+// Strides of a [B, H, N, D] operand in elements (D is contiguous).
+struct Strides {
+  int64_t b, h, n;
+};
 
-// K / V map with the two parity streams as a dimension: [D, ks, N/ks, BH], box [64, 1, kTileN, 1].
-// A tile is kTileN consecutive key tokens of one parity; rows of the other parity are skipped by
-// the stride, out-of-range tokens read as zero and the next head is never touched.
-int encode_kv_map(CUtensorMap* tm, const void* ptr, int BH, int N, int D, int ks, int dtype) {
+// Q map: [D, N, H, B] with the operand's own strides, box [64, 128, 1, 1]
+int encode_q_map(CUtensorMap* tm, const void* ptr, int B, int H, int N, int D, Strides st, int dtype) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return SPSATTN_ERR_DRIVER;
-  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)ks, (cuuint64_t)(N / ks), (cuuint64_t)BH};
-  cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)ks * D * 2, (cuuint64_t)N * D * 2};
-  cuuint32_t box[4] = {64, 1, (cuuint32_t)kTileN, 1};
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)st.n * 2, (cuuint64_t)st.h * 2, (cuuint64_t)st.b * 2};
+  cuuint32_t box[4] = {64, 128, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(tm, dtype == SPSATTN_DTYPE_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
@@ -93,6 +80,31 @@ int encode_kv_map(CUtensorMap* tm, const void* ptr, int BH, int N, int D, int ks
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+// K / V map with the two parity streams as a dimension: [D, ks, N/ks, H, B], box
+// [64, 1, kTileN, 1, 1].  A tile is kTileN consecutive key tokens of one parity; rows of the
+// other parity are skipped by the stride, out-of-range tokens read as zero and the next head
+// is never touched.
+int encode_kv_map(CUtensorMap* tm, const void* ptr, int B, int H, int N, int D, int ks, Strides st,
+                  int dtype) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return SPSATTN_ERR_DRIVER;
+  cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)ks, (cuuint64_t)(N / ks), (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[4] = {(cuuint64_t)st.n * 2, (cuuint64_t)ks * st.n * 2, (cuuint64_t)st.h * 2,
+                           (cuuint64_t)st.b * 2};
+  cuuint32_t box[5] = {64, 1, (cuuint32_t)kTileN, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(tm, dtype == SPSATTN_DTYPE_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                   5, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+bool strides_ok(Strides st, int D) {
+  return st.n >= D && st.h >= D && st.b >= D && (st.n % 8) == 0 && (st.h % 8) == 0 && (st.b % 8) == 0;
 }
 
 template <int D, bool FP16>
@@ -200,12 +212,15 @@ size_t spsattn_prefill_workspace_bytes(int B, int H, int N, int D) {
   return prefill_ws_mono_bytes(B) + align_up((size_t)B * N * sizeof(int), 256);
 }
 
-int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
-                        const void* doc_ids, int doc_is_i64, int64_t doc_stride_b, int64_t doc_stride_t,
-                        int B, int H, int N, int D, int dtype, float sm_scale, int persistent_parity,
-                        int temporary_window, int persistent_window, int mask_flags, void* workspace,
-                        size_t workspace_bytes, int* device_status, void* stream) {
-  if (!q || !k || !v || !o) return SPSATTN_ERR_ARG;
+int spsattn_prefill_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse,
+                                const int64_t* q_strides, const int64_t* k_strides,
+                                const int64_t* v_strides, const int64_t* o_strides, const void* doc_ids,
+                                int doc_is_i64, int64_t doc_stride_b, int64_t doc_stride_t, int B, int H,
+                                int N, int D, int dtype, float sm_scale, int persistent_parity,
+                                int temporary_window, int persistent_window, int mask_flags,
+                                void* workspace, size_t workspace_bytes, int* device_status,
+                                void* stream) {
+  if (!q || !k || !v || !o || !q_strides || !k_strides || !v_strides || !o_strides) return SPSATTN_ERR_ARG;
   if (B <= 0 || H <= 0 || N <= 0) return SPSATTN_ERR_ARG;
   if (dtype != SPSATTN_DTYPE_BF16 && dtype != SPSATTN_DTYPE_FP16) return SPSATTN_ERR_ARG;
   if (persistent_parity != SPSATTN_PARITY_EVEN && persistent_parity != SPSATTN_PARITY_ODD &&
@@ -216,6 +231,12 @@ int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, fl
   if (persistent_parity != SPSATTN_PARITY_NONE && (N & 1)) return SPSATTN_ERR_ODD_LENGTH;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return SPSATTN_ERR_ALIGN;
   if ((long long)B * H > 0x7fffffffLL / 64) return SPSATTN_ERR_TOO_LARGE;
+  const Strides sq = {q_strides[0], q_strides[1], q_strides[2]};
+  const Strides sk = {k_strides[0], k_strides[1], k_strides[2]};
+  const Strides sv = {v_strides[0], v_strides[1], v_strides[2]};
+  const Strides so = {o_strides[0], o_strides[1], o_strides[2]};
+  if (!strides_ok(sq, D) || !strides_ok(sk, D) || !strides_ok(sv, D) || !strides_ok(so, D))
+    return SPSATTN_ERR_ALIGN;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
   int *lo = nullptr, *mono = nullptr;
@@ -229,12 +250,15 @@ int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, fl
 
   if (D == 64 || D == 128) {
     CUtensorMap tq, tk, tv;
-    if ((rc = encode_q_map(&tq, q, B * H, N, D, dtype)) != 0) return rc;
-    if ((rc = encode_kv_map(&tk, k, B * H, N, D, mask.ks, dtype)) != 0) return rc;
-    if ((rc = encode_kv_map(&tv, v, B * H, N, D, mask.ks, dtype)) != 0) return rc;
+    if ((rc = encode_q_map(&tq, q, B, H, N, D, sq, dtype)) != 0) return rc;
+    if ((rc = encode_kv_map(&tk, k, B, H, N, D, mask.ks, sk, dtype)) != 0) return rc;
+    if ((rc = encode_kv_map(&tv, v, B, H, N, D, mask.ks, sv, dtype)) != 0) return rc;
     PrefillParams prm;
     memset(&prm, 0, sizeof(prm));
     prm.o = o;
+    prm.o_stride_b = so.b;
+    prm.o_stride_h = so.h;
+    prm.o_stride_n = so.n;
     prm.lse = lse;
     prm.docs = doc_ids;
     prm.doc_stride_b = doc_stride_b;
@@ -257,6 +281,10 @@ int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, fl
     return fp16 ? launch_prefill_sm100<128, true>(tq, tk, tv, prm, st)
                 : launch_prefill_sm100<128, false>(tq, tk, tv, prm, st);
   }
+  // the CUDA-core kernel for the other head dims reads dense [B, H, N, D] operands only
+  const Strides dense = {(int64_t)H * N * D, (int64_t)N * D, (int64_t)D};
+  auto is_dense = [&](Strides x) { return x.b == dense.b && x.h == dense.h && x.n == dense.n; };
+  if (!is_dense(sq) || !is_dense(sk) || !is_dense(sv) || !is_dense(so)) return SPSATTN_ERR_ALIGN;
   dim3 grid((N + 3) / 4, B * H);
   const size_t smem = 4 * (size_t)D * sizeof(float);
   if (fp16)
@@ -266,6 +294,18 @@ int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, fl
     prefill_generic_kernel<false><<<grid, 128, smem, st>>>(q, k, v, o, lse, doc_ids, doc_is_i64, doc_stride_b,
                                                            doc_stride_t, lo, mono, H, N, D, mask, scale_log2);
   return (int)cudaGetLastError();
+}
+
+int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                        const void* doc_ids, int doc_is_i64, int64_t doc_stride_b, int64_t doc_stride_t,
+                        int B, int H, int N, int D, int dtype, float sm_scale, int persistent_parity,
+                        int temporary_window, int persistent_window, int mask_flags, void* workspace,
+                        size_t workspace_bytes, int* device_status, void* stream) {
+  const int64_t dense[3] = {(int64_t)H * N * D, (int64_t)N * D, (int64_t)D};
+  return spsattn_prefill_fwd_strided(q, k, v, o, lse, dense, dense, dense, dense, doc_ids, doc_is_i64,
+                                     doc_stride_b, doc_stride_t, B, H, N, D, dtype, sm_scale,
+                                     persistent_parity, temporary_window, persistent_window, mask_flags,
+                                     workspace, workspace_bytes, device_status, stream);
 }
 
 int spsattn_debug_visibility(uint8_t* vis, const void* doc_ids, int doc_is_i64, int64_t doc_stride_b,

@@ -255,3 +255,27 @@ def test_argument_errors():
         sps_b200.sps_sliding_attention(q, q, q, 0.125, 2)           # forward only
     with pytest.raises(RuntimeError):
         sps_b200.sps_sliding_attention(q.detach().cpu(), q.detach().cpu(), q.detach().cpu(), 0.125, 2)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_token_major_and_fused_projection_views_need_no_copy(d):
+    """The layouts the reference's modules actually pass (sps/core.py:45-55): q, k, v as transposed
+    views of token-major [B, N, H, D] data, here even as slices of one fused [B, N, 3*H*D]
+    projection buffer.  The kernel reads them in place and returns token-major output."""
+    import sps_b200
+    dev = _dev()
+    B, H, N, w = 2, 3, 456, 9
+    g = torch.Generator().manual_seed(d)
+    qkv = torch.randn(B, N, 3 * H * d, generator=g).bfloat16().to(dev)
+    q, k, v = (x.view(B, N, H, d).transpose(1, 2) for x in qkv.split(H * d, dim=2))
+    assert not q.is_contiguous()
+    docs = torch.from_numpy(_random_docs(np.random.default_rng(1), B, N, "per_token")).to(dev)
+    out = sps_b200.sps_sliding_attention(q, k, v, 1 / math.sqrt(d), w, documents_idx_BxT=docs)
+    sps_b200.check_device_status()
+    assert out.shape == (B, H, N, d)
+    assert out.transpose(1, 2).is_contiguous()          # y.transpose(1, 2).contiguous() is free
+    ref = orc.prefill_attention(q.cpu(), k.cpu(), v.cpu(), 1 / math.sqrt(d), temporary_window=w, docs=docs.cpu())
+    _check(out, ref)
+    dense = sps_b200.sps_sliding_attention(q.contiguous(), k.contiguous(), v.contiguous(), 1 / math.sqrt(d), w,
+                                           documents_idx_BxT=docs)
+    assert torch.equal(dense, out)                      # same kernel, same tiles: bit-identical
