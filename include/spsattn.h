@@ -20,6 +20,7 @@
  *                            triton_reverse_sps_flash_attention.py:242-331, triton_full_flash_attention.py:204-283
  *   spsattn_decode_fwd       src/modeling/models/utils/decode_attention.py:483-594 (q=2), :393-480 (q=1)
  *   spsattn_kv_update        src/modeling/models/utils/decode_attention_fast.py:139-221
+ *   spsattn_fill_decode_caches  src/modeling/models/reverse_sps/inference.py:568-613
  */
 #ifndef SPSATTN_H_
 #define SPSATTN_H_
@@ -199,6 +200,24 @@ int spsattn_kv_update(void* nw_k, void* nw_v, int64_t* nw_len, int64_t* nw_pos,
                       const int8_t* active,
                       int S, int H, int D, int window_storage, int retained_storage,
                       int window_tokens, int elem_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Prefill -> decode hand-over for one layer (src/modeling/models/reverse_sps/inference.py:568-613,
+ * there a Python loop over batch rows with host syncs): for every batch row the tokens selected by
+ * doc_mask [B, T] (bytes; the prompt's last document) are compacted in order; the K/V rows of
+ * parity `retained_slot` of those tokens go to the retained cache [B,H,retained_storage,D] rows
+ * 0..doc_len-1 and br_len[b,:] = doc_len; the rows of parity `window_slot` of the last
+ * min(window_tokens, doc_len) of them go to the ring [B,H,window_storage,D] rows 0.., with
+ * nw_len[b] = that count and nw_pos[b] = 0.  Rows without a selected token are left untouched.
+ * k, v: [B, 2T, H, D] 16-bit elements in the cache dtype, strides in elements (D contiguous,
+ * multiples of 8), T < 32768.  window_tokens <= 0: retained part only.
+ * ------------------------------------------------------------------------------------------- */
+int spsattn_fill_decode_caches(const void* k, const void* v, int64_t stride_b, int64_t stride_n,
+                               int64_t stride_h, const uint8_t* doc_mask,
+                               void* br_k, void* br_v, int64_t* br_len,
+                               void* nw_k, void* nw_v, int64_t* nw_len, int64_t* nw_pos,
+                               int B, int T, int H, int D, int retained_storage, int window_storage,
+                               int window_tokens, int retained_slot, int window_slot, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Test hook: the boolean visibility the prefill kernels apply, evaluated on the device with the

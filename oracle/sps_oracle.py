@@ -362,3 +362,30 @@ def kv_update(nw_k, nw_v, nw_len, nw_pos, br_k, br_v, br_len,
                 br_k[b, h, ln] = k_retained[b, h].to(br_k.dtype)
                 br_v[b, h, ln] = v_retained[b, h].to(br_v.dtype)
                 br_len[b, h] = ln + 1
+
+
+def fill_decode_caches(k, v, doc_mask, br_k, br_v, br_len, nw_k, nw_v, nw_len, nw_pos,
+                       window_tokens: int, retained_slot: int, window_slot: int) -> None:
+    """In-place prefill -> decode hand-over of one layer.
+
+    Follows src/modeling/models/reverse_sps/inference.py:568-613: per batch row, the positions
+    selected by ``doc_mask`` are compacted; retained-slot rows fill the retained cache and set its
+    lengths; window-slot rows of the last ``window_tokens`` positions fill the ring, ``pos = 0``.
+    k, v: [B, 2T, H, D].
+    """
+    B = k.shape[0]
+    for b in range(B):
+        pos = torch.nonzero(doc_mask[b].bool()).flatten()
+        n = int(pos.numel())
+        if n == 0:
+            continue
+        br_k[b, :, :n] = k[b, 2 * pos + retained_slot].transpose(0, 1).to(br_k.dtype)
+        br_v[b, :, :n] = v[b, 2 * pos + retained_slot].transpose(0, 1).to(br_v.dtype)
+        br_len[b, :] = n
+        if window_tokens > 0:
+            wp = pos[-window_tokens:]
+            wl = int(wp.numel())
+            nw_k[b, :, :wl] = k[b, 2 * wp + window_slot].transpose(0, 1).to(nw_k.dtype)
+            nw_v[b, :, :wl] = v[b, 2 * wp + window_slot].transpose(0, 1).to(nw_v.dtype)
+            nw_len[b] = wl
+            nw_pos[b] = 0

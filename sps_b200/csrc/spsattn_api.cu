@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "../../include/spsattn.h"
+#include "cache_fill.cuh"
 #include "decode.cuh"
 #include "kv_update.cuh"
 #include "prefill_aux.cuh"
@@ -410,6 +411,50 @@ int spsattn_decode_fwd(const void* q, int nq, float* out, const spsattn_segment*
     case 128: return launch_decode_d<128>(prm, nq, fp16, st);
     default: return launch_decode_d<256>(prm, nq, fp16, st);
   }
+}
+
+// ------------------------------------------------------------------------------- prefill -> caches
+
+int spsattn_fill_decode_caches(const void* k, const void* v, int64_t stride_b, int64_t stride_n,
+                               int64_t stride_h, const uint8_t* doc_mask, void* br_k, void* br_v,
+                               int64_t* br_len, void* nw_k, void* nw_v, int64_t* nw_len, int64_t* nw_pos,
+                               int B, int T, int H, int D, int retained_storage, int window_storage,
+                               int window_tokens, int retained_slot, int window_slot, void* stream) {
+  if (!k || !v || !doc_mask || !br_k || !br_v || !br_len) return SPSATTN_ERR_ARG;
+  if (B <= 0 || T <= 0 || H <= 0 || D <= 0 || retained_storage < 0) return SPSATTN_ERR_ARG;
+  if (T >= 32768) return SPSATTN_ERR_TOO_LARGE;
+  if ((retained_slot != 0 && retained_slot != 1) || (window_slot != 0 && window_slot != 1))
+    return SPSATTN_ERR_ARG;
+  if (window_tokens > 0 && (!nw_k || !nw_v || !nw_len || !nw_pos || window_storage <= 0))
+    return SPSATTN_ERR_ARG;
+  if ((D % 8) || (stride_b % 8) || (stride_n % 8) || (stride_h % 8) || stride_h < D) return SPSATTN_ERR_ALIGN;
+  if (!aligned16(k) || !aligned16(v) || !aligned16(br_k) || !aligned16(br_v)) return SPSATTN_ERR_ALIGN;
+  if (window_tokens > 0 && (!aligned16(nw_k) || !aligned16(nw_v))) return SPSATTN_ERR_ALIGN;
+  CacheFillParams p;
+  p.k = reinterpret_cast<const uint16_t*>(k);
+  p.v = reinterpret_cast<const uint16_t*>(v);
+  p.stride_b = stride_b;
+  p.stride_n = stride_n;
+  p.stride_h = stride_h;
+  p.doc_mask = doc_mask;
+  p.br_k = reinterpret_cast<uint16_t*>(br_k);
+  p.br_v = reinterpret_cast<uint16_t*>(br_v);
+  p.br_len = br_len;
+  p.nw_k = reinterpret_cast<uint16_t*>(nw_k);
+  p.nw_v = reinterpret_cast<uint16_t*>(nw_v);
+  p.nw_len = nw_len;
+  p.nw_pos = nw_pos;
+  p.T = T;
+  p.H = H;
+  p.D = D;
+  p.retained_storage = retained_storage;
+  p.window_storage = window_storage;
+  p.window_tokens = window_tokens > 0 ? window_tokens : 0;
+  p.retained_slot = retained_slot;
+  p.window_slot = window_slot;
+  dim3 grid((T + kFillChunk - 1) / kFillChunk, B);
+  cache_fill_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return (int)cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------- allocation-free decode

@@ -238,3 +238,45 @@ def fused_sps_kv_update(*, nw_k: Tensor, nw_v: Tensor, nw_len: Tensor, nw_pos: T
             int(br_k.size(2)), int(window_tokens), br_k.element_size(),
             torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "spsattn_kv_update")
+
+
+def fill_decode_caches(k_Bx2TxHxD: Tensor, v_Bx2TxHxD: Tensor, current_doc_mask_BxT: Tensor, *,
+                       br_k: Tensor, br_v: Tensor, br_len: Tensor,
+                       nw_k: Optional[Tensor] = None, nw_v: Optional[Tensor] = None,
+                       nw_len: Optional[Tensor] = None, nw_pos: Optional[Tensor] = None,
+                       window_tokens: int = 0, retained_slot: int = 0, window_slot: int = 1) -> None:
+    """Fill one layer's decode caches from the prefill K/V in one launch, no host sync
+    (what reverse_sps/inference.py:568-613 does with a Python loop over batch rows).
+
+    ``retained_slot`` / ``window_slot``: parity of the doubled-sequence row that feeds the retained
+    cache / the ring (SPS: 0 and 1; Reverse-SPS and Delayed-State: 1 and 0).
+    """
+    lib = _lib.load()
+    B, two_t, H, D = k_Bx2TxHxD.shape
+    T = two_t // 2
+    k = k_Bx2TxHxD.to(br_k.dtype)
+    v = v_Bx2TxHxD.to(br_v.dtype)
+    if k.stride(3) != 1 or any(s % 8 for s in k.stride()[:3]):
+        k = k.contiguous()
+    if v.stride() != k.stride():
+        v = v.contiguous()
+        k = k.contiguous()
+    assert br_k.element_size() == 2, "caches hold 16-bit elements"
+    assert br_k.is_contiguous() and br_v.is_contiguous() and br_len.is_contiguous()
+    assert br_len.dtype == torch.int64 and tuple(br_len.shape) == (B, H)
+    mask = current_doc_mask_BxT.to(torch.uint8).contiguous()
+    assert tuple(mask.shape) == (B, T)
+    ring = [None, None, None, None]
+    window_storage = 0
+    if window_tokens > 0:
+        assert nw_k.is_contiguous() and nw_v.is_contiguous()
+        assert nw_len.dtype == torch.int64 and nw_pos.dtype == torch.int64
+        window_storage = int(nw_k.size(2))
+        ring = [nw_k.data_ptr(), nw_v.data_ptr(), nw_len.data_ptr(), nw_pos.data_ptr()]
+    with torch.cuda.device(k.device):
+        rc = lib.spsattn_fill_decode_caches(
+            k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1), k.stride(2), mask.data_ptr(),
+            br_k.data_ptr(), br_v.data_ptr(), br_len.data_ptr(), ring[0], ring[1], ring[2], ring[3],
+            B, T, H, D, int(br_k.size(2)), window_storage, int(window_tokens), int(retained_slot),
+            int(window_slot), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "spsattn_fill_decode_caches")

@@ -14,7 +14,8 @@ It imports, unmodified, from the reference:
   * ``masked_kv_attention`` (SDPA path)    src/modeling/models/utils/decode_attention.py:597-704
   * ``window_score_mod_factory``           src/modeling/tests/_sliding_window_reference.py:15-34
   * the eager cache update methods         src/modeling/models/reverse_sps/inference.py:137-167, :240-268
-    through the reference's own tiny Delayed-State test model.
+    and the prefill -> decode hand-over     src/modeling/models/reverse_sps/inference.py:568-613
+    through the reference's own tiny Delayed-State / SPS test models.
 
 Every case stores its inputs (bf16/fp16 values widened to fp32, integer tensors
 as int64) next to the reference output so the tests need nothing but numpy.
@@ -225,6 +226,37 @@ def kv_update_cases():
     put("kvu_br_len", state.predict_retained.len[0])
 
 
+def cache_fill_cases():
+    """The reference's own hand-over (reverse_sps/inference.py:568-613) on its tiny SPS and
+    Delayed-State test models: left padding, a finished earlier document, a one-token document."""
+    from modeling.tests.models.delayed_state.test_forward_efficient import _make_delayed_state_model
+    from modeling.tests.models.sps.test_dense_only import _make_sps_model
+    for tag, make, w in (("ds", lambda: _make_delayed_state_model(window_size=3), 3),
+                         ("sps", _make_sps_model, 2)):
+        torch.manual_seed(21)
+        bsz, t = 4, 9
+        model = make()
+        nh = model.config.n_head
+        hd = model.config.hidden_size // nh
+        state = model._build_decode_state(batch_size=bsz, max_tokens=t + 2, device=torch.device("cpu"),
+                                          attn_dtype=torch.float32)
+        k = torch.randn(bsz, 2 * t, nh, hd).bfloat16().float()
+        v = torch.randn(bsz, 2 * t, nh, hd).bfloat16().float()
+        mask = torch.zeros(bsz, t, dtype=torch.bool)
+        mask[0, :] = True
+        mask[1, 4:] = True
+        mask[2, -1] = True
+        mask[3, 2:4] = True
+        model._materialize_prefill_layer_state(state, 0, k, v, mask)
+        put(f"fill_{tag}_k", k), put(f"fill_{tag}_v", v), put(f"fill_{tag}_mask", mask.long())
+        put(f"fill_{tag}_window", np.int64(w))
+        put(f"fill_{tag}_slots", np.array([model._retained_slot_index, model._window_slot_index]))
+        put(f"fill_{tag}_br_k", state.predict_retained.k[0]), put(f"fill_{tag}_br_v", state.predict_retained.v[0])
+        put(f"fill_{tag}_br_len", state.predict_retained.len[0])
+        put(f"fill_{tag}_nw_k", state.normal_window.k[0]), put(f"fill_{tag}_nw_v", state.normal_window.v[0])
+        put(f"fill_{tag}_nw_len", state.normal_window.len[0]), put(f"fill_{tag}_nw_pos", state.normal_window.pos[0])
+
+
 if __name__ == "__main__":
     with torch.no_grad():
         sps_cases()
@@ -233,6 +265,7 @@ if __name__ == "__main__":
         decode_cases()
         visibility_cases()
         kv_update_cases()
+        cache_fill_cases()
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
     np.savez_compressed(path, **OUT)
     print(f"wrote {path}: {len(OUT)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")

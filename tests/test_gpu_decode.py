@@ -209,3 +209,68 @@ def test_decode_argument_errors():
         sps_b200.segmented_q2_attention(q.cpu(), [sps_b200.KVSegment(k, k, ln)], **kw)
     with pytest.raises(RuntimeError):
         sps_b200.segmented_q2_attention(q, [sps_b200.KVSegment(k, k, ln.cpu())], **kw)
+
+
+@pytest.mark.parametrize("tag", ["ds", "sps"])
+def test_cache_fill_matches_reference_vectors(golden, tag):
+    """Prefill -> decode hand-over against the reference's own Python loop
+    (reverse_sps/inference.py:568-613), bit-exact: it is a gather of 16-bit rows."""
+    import sps_b200
+    dev, bf = _dev(), torch.bfloat16
+    g = {k[len(f"fill_{tag}_"):]: v for k, v in golden.items() if k.startswith(f"fill_{tag}_")}
+    w = int(g["window"])
+    rs, ws = (int(x) for x in g["slots"])
+    B, H, cap, D = g["br_k"].shape
+    canary = 7.0
+    br_k, br_v = (torch.full((B, H, cap, D), canary, device=dev, dtype=bf) for _ in range(2))
+    nw_k, nw_v = (torch.full(g["nw_k"].shape, canary, device=dev, dtype=bf) for _ in range(2))
+    br_len = torch.full((B, H), -5, dtype=torch.long, device=dev)
+    nw_len, nw_pos = (torch.full((B,), -5, dtype=torch.long, device=dev) for _ in range(2))
+    sps_b200.fill_decode_caches(_c(g["k"], bf), _c(g["v"], bf), _c(g["mask"]).bool(), br_k=br_k, br_v=br_v,
+                                br_len=br_len, nw_k=nw_k, nw_v=nw_v, nw_len=nw_len, nw_pos=nw_pos,
+                                window_tokens=w, retained_slot=rs, window_slot=ws)
+    want_len = g["br_len"]
+    for b in range(B):
+        n = int(want_len[b, 0])
+        assert br_len[b].tolist() == [n] * H
+        assert torch.equal(br_k[b, :, :n].float().cpu(), torch.from_numpy(g["br_k"][b, :, :n]))
+        assert torch.equal(br_v[b, :, :n].float().cpu(), torch.from_numpy(g["br_v"][b, :, :n]))
+        assert float((br_k[b, :, n:].float() - canary).abs().max()) == 0 if n < cap else True   # untouched
+        wl = int(g["nw_len"][b])
+        assert int(nw_len[b]) == wl and int(nw_pos[b]) == 0
+        assert torch.equal(nw_k[b, :, :wl].float().cpu(), torch.from_numpy(g["nw_k"][b, :, :wl]))
+        assert torch.equal(nw_v[b, :, :wl].float().cpu(), torch.from_numpy(g["nw_v"][b, :, :wl]))
+
+
+def test_cache_fill_large_ragged_matches_oracle():
+    """Left-padded prompts of different lengths with earlier documents, strided K/V views (slices
+    of a fused projection buffer), T not a multiple of the block's chunk, an empty selection."""
+    import sps_b200
+    dev, bf = _dev(), torch.bfloat16
+    B, T, H, D, w = 5, 333, 4, 64, 64
+    g = torch.Generator().manual_seed(8)
+    qkv = torch.randn(B, 2 * T, 3 * H * D, generator=g).to(bf)
+    k, v = (x.view(B, 2 * T, H, D) for x in qkv.split(H * D, dim=2)[1:])
+    mask = torch.zeros(B, T, dtype=torch.bool)
+    for b, start in enumerate((0, 100, 332, 290)):
+        mask[b, start:] = True
+    cap = T + 8
+    outs = []
+    for where in ("cpu", "cuda"):
+        br_k, br_v = (torch.zeros(B, H, cap, D, dtype=bf) for _ in range(2))
+        nw_k, nw_v = (torch.zeros(B, H, w, D, dtype=bf) for _ in range(2))
+        br_len = torch.zeros(B, H, dtype=torch.long)
+        nw_len, nw_pos = torch.zeros(B, dtype=torch.long), torch.full((B,), 3, dtype=torch.long)
+        if where == "cpu":
+            orc.fill_decode_caches(k, v, mask, br_k, br_v, br_len, nw_k, nw_v, nw_len, nw_pos, w, 0, 1)
+        else:
+            br_k, br_v, nw_k, nw_v, br_len, nw_len, nw_pos = (x.to(dev) for x in (br_k, br_v, nw_k, nw_v, br_len,
+                                                                               nw_len, nw_pos))
+            kd, vd = (x.view(B, 2 * T, H, D) for x in qkv.to(dev).split(H * D, dim=2)[1:])
+            assert not kd.is_contiguous()
+            sps_b200.fill_decode_caches(kd, vd, mask.to(dev), br_k=br_k, br_v=br_v, br_len=br_len,
+                                        nw_k=nw_k, nw_v=nw_v, nw_len=nw_len, nw_pos=nw_pos, window_tokens=w,
+                                        retained_slot=0, window_slot=1)
+        outs.append([x.cpu() for x in (br_k, br_v, br_len, nw_k, nw_v, nw_len, nw_pos)])
+    for a, b_ in zip(*outs):
+        assert torch.equal(a, b_)

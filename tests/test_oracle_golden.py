@@ -144,3 +144,20 @@ def test_run_starts_and_monotone():
     lo = orc.run_starts(d)
     i, j = np.arange(7)[:, None], np.arange(7)[None, :]
     assert np.array_equal((d[:, None] == d[None, :]) & (j <= i), (j >= lo[:, None]) & (j <= i))
+
+
+@pytest.mark.parametrize("tag", ["ds", "sps"])
+def test_cache_fill_matches_reference_handover(golden, tag):
+    g = {k[len(f"fill_{tag}_"):]: v for k, v in golden.items() if k.startswith(f"fill_{tag}_")}
+    w = int(g["window"])
+    rs, ws = (int(x) for x in g["slots"])
+    br_k, br_v = torch.zeros(g["br_k"].shape), torch.zeros(g["br_v"].shape)
+    nw_k, nw_v = torch.zeros(g["nw_k"].shape), torch.zeros(g["nw_v"].shape)
+    br_len = torch.zeros(g["br_len"].shape, dtype=torch.long)
+    nw_len = torch.zeros(g["nw_len"].shape, dtype=torch.long)
+    nw_pos = torch.zeros(g["nw_pos"].shape, dtype=torch.long)
+    orc.fill_decode_caches(T(g["k"]), T(g["v"]), T(g["mask"]), br_k, br_v, br_len, nw_k, nw_v, nw_len, nw_pos,
+                           w, rs, ws)
+    for name, val in (("br_k", br_k), ("br_v", br_v), ("br_len", br_len), ("nw_k", nw_k), ("nw_v", nw_v),
+                      ("nw_len", nw_len), ("nw_pos", nw_pos)):
+        assert np.array_equal(val.numpy(), g[name]), name
