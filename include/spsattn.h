@@ -21,6 +21,7 @@
  *   spsattn_decode_fwd       src/modeling/models/utils/decode_attention.py:483-594 (q=2), :393-480 (q=1)
  *   spsattn_kv_update        src/modeling/models/utils/decode_attention_fast.py:139-221
  *   spsattn_fill_decode_caches  src/modeling/models/reverse_sps/inference.py:568-613
+ *   spsattn_rope_cast        src/modeling/models/model.py:201-230 + sps/core.py:53-55
  */
 #ifndef SPSATTN_H_
 #define SPSATTN_H_
@@ -200,6 +201,20 @@ int spsattn_kv_update(void* nw_k, void* nw_v, int64_t* nw_len, int64_t* nw_pos,
                       const int8_t* active,
                       int S, int H, int D, int window_storage, int retained_storage,
                       int window_tokens, int elem_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Rotary embedding + cast for q or k (rotate = 1) or plain cast for v (rotate = 0), writing the
+ * 16-bit operand the attention kernels read (src/modeling/models/model.py:201-230 followed by the
+ * bf16 cast of src/modeling/models/sps/core.py:53-55).  x: [B, N, H, D] view, x_dtype 0 bf16,
+ * 1 fp16, 2 fp32, strides in elements (D contiguous).  freqs_cis: complex64 as (cos, sin) float
+ * pairs, [N, D/2] (freqs_stride_b = 0) or [B, N, D/2] (freqs_stride_b = N * D/2, in complex
+ * elements).  Adjacent elements (2i, 2i+1) form the complex number that is multiplied by
+ * freqs_cis[n, i] in fp32.  out: 16-bit rows with its own strides.  D multiple of 8.
+ * ------------------------------------------------------------------------------------------- */
+int spsattn_rope_cast(const void* x, int x_dtype, int64_t x_stride_b, int64_t x_stride_n,
+                      int64_t x_stride_h, const float* freqs_cis, int64_t freqs_stride_b,
+                      void* out, int out_dtype, int64_t out_stride_b, int64_t out_stride_n,
+                      int64_t out_stride_h, int B, int N, int H, int D, int rotate, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Prefill -> decode hand-over for one layer (src/modeling/models/reverse_sps/inference.py:568-613,

@@ -389,3 +389,19 @@ def fill_decode_caches(k, v, doc_mask, br_k, br_v, br_len, nw_k, nw_v, nw_len, n
             nw_v[b, :, :wl] = v[b, 2 * wp + window_slot].transpose(0, 1).to(nw_v.dtype)
             nw_len[b] = wl
             nw_pos[b] = 0
+
+
+def rope_cast(x: torch.Tensor, freqs_cis: Optional[torch.Tensor], out_dtype=torch.bfloat16) -> torch.Tensor:
+    """Rotary embedding of a [B, N, H, D] projection followed by the operand cast.
+
+    Follows src/modeling/models/model.py:201-230 (pairs viewed as complex, multiplied by
+    ``freqs_cis`` broadcast over heads, viewed back as real, ``type_as`` the input) and the bf16
+    cast of src/modeling/models/sps/core.py:53-55.  ``freqs_cis``: complex64 [N, D/2] or
+    [B, N, D/2]; None = cast only.
+    """
+    if freqs_cis is None:
+        return x.to(out_dtype)
+    x_ = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
+    f = freqs_cis.unsqueeze(2) if freqs_cis.dim() == 3 else freqs_cis.view(1, x.shape[1], 1, -1)
+    out = torch.view_as_real(x_ * f).flatten(3)
+    return out.type_as(x).to(out_dtype)

@@ -7,7 +7,7 @@ update (``decode``), and ``install()`` which rebinds the reference model classes
 
 from . import _lib
 from .attention import (check_device_status, full_attention, prefill_attention,
-                        reverse_sps_sliding_attention, sps_sliding_attention)
+                        reverse_sps_sliding_attention, rope_cast, sps_sliding_attention)
 from .decode import (KVSegment, PackedKVSegment, decode_attention, fill_decode_caches, fused_sps_kv_update,
                      masked_kv_attention, segmented_q1_attention, segmented_q2_attention,
                      triton_segmented_q2_attention)
@@ -17,6 +17,6 @@ __all__ = [
     "KVSegment", "PackedKVSegment", "check_device_status", "decode_attention", "fill_decode_caches",
     "full_attention",
     "fused_sps_kv_update", "install", "masked_kv_attention", "prefill_attention",
-    "reverse_sps_sliding_attention", "segmented_q1_attention", "segmented_q2_attention",
+    "reverse_sps_sliding_attention", "rope_cast", "segmented_q1_attention", "segmented_q2_attention",
     "sps_sliding_attention", "triton_segmented_q2_attention",
 ]

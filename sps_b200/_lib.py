@@ -22,7 +22,7 @@ EXPORTS = (
     "spsattn_version", "spsattn_strerror",
     "spsattn_prefill_workspace_bytes", "spsattn_prefill_fwd", "spsattn_prefill_fwd_strided",
     "spsattn_decode_workspace_bytes", "spsattn_decode_fwd", "spsattn_decode_fwd_noalloc",
-    "spsattn_kv_update", "spsattn_fill_decode_caches", "spsattn_debug_visibility",
+    "spsattn_kv_update", "spsattn_fill_decode_caches", "spsattn_rope_cast", "spsattn_debug_visibility",
 )
 
 
@@ -85,6 +85,9 @@ def load() -> C.CDLL:
     lib.spsattn_fill_decode_caches.restype = i32
     lib.spsattn_fill_decode_caches.argtypes = [vp, vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp,
                                                i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+    lib.spsattn_rope_cast.restype = i32
+    lib.spsattn_rope_cast.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, i32, i64, i64, i64,
+                                      i32, i32, i32, i32, i32, vp]
     lib.spsattn_debug_visibility.restype = i32
     lib.spsattn_debug_visibility.argtypes = [vp, vp, i32, i64, i64, i32, i32, i32, i32, i32, i32, vp, sz, vp]
     _lib = lib

@@ -185,3 +185,42 @@ def visibility(n_ctx: int, *, persistent_parity: int, temporary_window: int = 0,
             None if ws is None else ws.data_ptr(), ws_bytes, torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "spsattn_debug_visibility")
     return vis.bool()
+
+
+_X_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+def rope_cast(x_BxNxHxD: torch.Tensor, freqs_cis: Optional[torch.Tensor], *,
+              out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Rotary embedding (``freqs_cis`` complex64 [N, D/2] or [B, N, D/2]; None = cast only) and
+    cast of one projection in a single pass.  Input: a [B, N, H, D] view (any of bf16 / fp16 /
+    fp32, row strides free).  Returns the attention operand as a [B, H, N, D] view of a
+    token-major buffer, which the prefill kernel reads in place.  One kernel instead of the
+    float / complex / multiply / cast / transpose chain of model.py:201-230 and sps/core.py:45-55.
+    """
+    lib = _lib.load()
+    x = x_BxNxHxD
+    if not x.is_cuda:
+        raise RuntimeError("rope_cast needs CUDA tensors")
+    B, N, H, D = x.shape
+    if x.dtype not in _X_DTYPES:
+        raise TypeError(f"unsupported projection dtype {x.dtype}")
+    align = 4 if x.dtype == torch.float32 else 8
+    if x.stride(3) != 1 or any(s % align for s in x.stride()[:3]) or x.data_ptr() % 16:
+        x = x.contiguous()
+    out = torch.empty((B, N, H, D), dtype=out_dtype, device=x.device)
+    f_ptr, f_sb = None, 0
+    if freqs_cis is not None:
+        f = torch.view_as_real(freqs_cis.to(torch.complex64)).contiguous()    # [.., N, D/2, 2] fp32
+        assert f.shape[-3:] == (N, D // 2, 2), f"freqs_cis must be [N, D/2] or [B, N, D/2], got {tuple(freqs_cis.shape)}"
+        if f.dim() == 4:
+            assert f.shape[0] == B
+            f_sb = N * (D // 2)
+        f_ptr = f.data_ptr()
+    with torch.cuda.device(x.device):
+        rc = lib.spsattn_rope_cast(x.data_ptr(), _X_DTYPES[x.dtype], x.stride(0), x.stride(1), x.stride(2),
+                                   f_ptr, f_sb, out.data_ptr(), _dtype_code(out), out.stride(0), out.stride(1),
+                                   out.stride(2), B, N, H, D, int(freqs_cis is not None),
+                                   torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "spsattn_rope_cast")
+    return out.transpose(1, 2)

@@ -14,6 +14,7 @@
 #include "kv_update.cuh"
 #include "prefill_aux.cuh"
 #include "prefill_sm100.cuh"
+#include "rope.cuh"
 
 using namespace spsattn;
 
@@ -411,6 +412,47 @@ int spsattn_decode_fwd(const void* q, int nq, float* out, const spsattn_segment*
     case 128: return launch_decode_d<128>(prm, nq, fp16, st);
     default: return launch_decode_d<256>(prm, nq, fp16, st);
   }
+}
+
+// ------------------------------------------------------------------------------------ rope + cast
+
+int spsattn_rope_cast(const void* x, int x_dtype, int64_t x_stride_b, int64_t x_stride_n,
+                      int64_t x_stride_h, const float* freqs_cis, int64_t freqs_stride_b, void* out,
+                      int out_dtype, int64_t out_stride_b, int64_t out_stride_n, int64_t out_stride_h,
+                      int B, int N, int H, int D, int rotate, void* stream) {
+  if (!x || !out || (rotate && !freqs_cis)) return SPSATTN_ERR_ARG;
+  if (B <= 0 || N <= 0 || H <= 0 || D <= 0) return SPSATTN_ERR_ARG;
+  if (x_dtype < 0 || x_dtype > 2) return SPSATTN_ERR_ARG;
+  if (out_dtype != SPSATTN_DTYPE_BF16 && out_dtype != SPSATTN_DTYPE_FP16) return SPSATTN_ERR_ARG;
+  if (D % 8) return SPSATTN_ERR_HEAD_DIM;
+  const int in_align = x_dtype == 2 ? 4 : 8;   // elements per 16 bytes
+  if ((x_stride_b % in_align) || (x_stride_n % in_align) || (x_stride_h % in_align) ||
+      (out_stride_b % 8) || (out_stride_n % 8) || (out_stride_h % 8) || (freqs_stride_b % 2))
+    return SPSATTN_ERR_ALIGN;
+  if (!aligned16(x) || !aligned16(out) || (rotate && !aligned16(freqs_cis))) return SPSATTN_ERR_ALIGN;
+  RopeParams p;
+  p.x = x;
+  p.x_dtype = x_dtype;
+  p.xs_b = x_stride_b;
+  p.xs_n = x_stride_n;
+  p.xs_h = x_stride_h;
+  p.freqs = reinterpret_cast<const float2*>(freqs_cis);
+  p.fs_b = freqs_stride_b;
+  p.out = reinterpret_cast<uint16_t*>(out);
+  p.out_fp16 = out_dtype == SPSATTN_DTYPE_FP16;
+  p.os_b = out_stride_b;
+  p.os_n = out_stride_n;
+  p.os_h = out_stride_h;
+  p.B = B;
+  p.N = N;
+  p.H = H;
+  p.D = D;
+  p.rotate = rotate;
+  const long long total = (long long)B * N * H * (D / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  rope_cast_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return (int)cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------- prefill -> caches

@@ -16,6 +16,7 @@ It imports, unmodified, from the reference:
   * the eager cache update methods         src/modeling/models/reverse_sps/inference.py:137-167, :240-268
     and the prefill -> decode hand-over     src/modeling/models/reverse_sps/inference.py:568-613
     through the reference's own tiny Delayed-State / SPS test models.
+  * ``apply_rotary_emb``, ``precompute_freqs_cis``  src/modeling/models/model.py:134-230
 
 Every case stores its inputs (bf16/fp16 values widened to fp32, integer tensors
 as int64) next to the reference output so the tests need nothing but numpy.
@@ -257,6 +258,26 @@ def cache_fill_cases():
         put(f"fill_{tag}_nw_len", state.normal_window.len[0]), put(f"fill_{tag}_nw_pos", state.normal_window.pos[0])
 
 
+def rope_cases():
+    """apply_rotary_emb + the bf16 operand cast, exactly as the attention modules chain them."""
+    from modeling.models.model import apply_rotary_emb, precompute_freqs_cis
+    g = torch.Generator().manual_seed(31)
+    B, N, H, D = 2, 12, 3, 16
+    fc = precompute_freqs_cis(D, 40)
+    for tag, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        xq = torch.randn(B, N, H, D, generator=g).to(dt)
+        xk = torch.randn(B, N, H, D, generator=g).to(dt)
+        pos = torch.arange(N // 2).repeat_interleave(2)                      # doubled sequence: shared positions
+        q1, k1 = apply_rotary_emb(xq, xk, freqs_cis=fc[pos])
+        per_seq = torch.stack([fc[pos], fc[pos + 7]])                        # [B, N, D/2]: left-padded batches
+        q2, k2 = apply_rotary_emb(xq, xk, freqs_cis=per_seq)
+        put(f"rope_{tag}_xq", xq), put(f"rope_{tag}_xk", xk)
+        put(f"rope_{tag}_q1", q1.to(torch.bfloat16)), put(f"rope_{tag}_k1", k1.to(torch.bfloat16))
+        put(f"rope_{tag}_q2", q2.to(torch.bfloat16)), put(f"rope_{tag}_k2", k2.to(torch.bfloat16))
+    OUT["rope_freqs"] = torch.view_as_real(fc).numpy()
+    put("rope_pos", pos)
+
+
 if __name__ == "__main__":
     with torch.no_grad():
         sps_cases()
@@ -266,6 +287,7 @@ if __name__ == "__main__":
         visibility_cases()
         kv_update_cases()
         cache_fill_cases()
+        rope_cases()
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
     np.savez_compressed(path, **OUT)
     print(f"wrote {path}: {len(OUT)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")

@@ -279,3 +279,57 @@ def test_token_major_and_fused_projection_views_need_no_copy(d):
     dense = sps_b200.sps_sliding_attention(q.contiguous(), k.contiguous(), v.contiguous(), 1 / math.sqrt(d), w,
                                            documents_idx_BxT=docs)
     assert torch.equal(dense, out)                      # same kernel, same tiles: bit-identical
+
+
+def _ulp_close(out, ref):
+    """bf16 results of fp32 math: identical up to a rare last-bit flip (products and sums of
+    the complex multiply may be fused differently on the two sides)."""
+    out, ref = out.float().cpu(), ref.float()
+    diff = (out - ref).abs()
+    ulp = ref.abs().clamp_min(1e-30) * 2.0 ** -7
+    assert bool((diff <= ulp).all()), float((diff / ulp).max())
+    assert float((diff > 0).float().mean()) <= 1e-3
+
+
+@pytest.mark.parametrize("tag,dt", [("f32", torch.float32), ("bf16", torch.bfloat16)])
+def test_rope_cast_matches_reference_vectors(golden, tag, dt):
+    import sps_b200
+    dev = _dev()
+    g = golden
+    fc = torch.view_as_complex(torch.from_numpy(g["rope_freqs"]).contiguous())
+    pos = torch.from_numpy(g["rope_pos"])
+    for which in ("q", "k"):
+        x = torch.from_numpy(g[f"rope_{tag}_x{which}"]).to(dt).to(dev)
+        out = sps_b200.rope_cast(x, fc[pos].to(dev))
+        assert out.shape == (x.shape[0], x.shape[2], x.shape[1], x.shape[3]) and out.dtype == torch.bfloat16
+        _ulp_close(out.transpose(1, 2), torch.from_numpy(g[f"rope_{tag}_{which}1"]))
+        out = sps_b200.rope_cast(x, torch.stack([fc[pos], fc[pos + 7]]).to(dev))
+        _ulp_close(out.transpose(1, 2), torch.from_numpy(g[f"rope_{tag}_{which}2"]))
+
+
+def test_rope_cast_feeds_the_attention_kernel_without_copies():
+    """Fused [B, N, 3*H*D] projection -> rope_cast(q), rope_cast(k), v in place -> attention:
+    the whole operand path of the reference's attention module (sps/core.py:41-79) with no
+    transposing copy, against the oracle."""
+    import sps_b200
+    dev = _dev()
+    B, T, H, D, w = 2, 150, 3, 64, 6
+    N = 2 * T
+    g = torch.Generator().manual_seed(4)
+    qkv = (torch.randn(B, N, 3 * H * D, generator=g) * 0.7).bfloat16().to(dev)
+    q, k, v = (x.view(B, N, H, D) for x in qkv.split(H * D, dim=2))
+    freqs = 1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.outer(torch.arange(T).repeat_interleave(2).float(), freqs)
+    fc = torch.polar(torch.ones_like(ang), ang).to(dev)
+    qr, kr = sps_b200.rope_cast(q, fc), sps_b200.rope_cast(k, fc)
+    vr = sps_b200.rope_cast(v, None)
+    docs = torch.from_numpy(_random_docs(np.random.default_rng(3), B, N, "per_token")).to(dev)
+    out = sps_b200.sps_sliding_attention(qr, kr, vr, 1 / math.sqrt(D), w, documents_idx_BxT=docs)
+    out2 = sps_b200.sps_sliding_attention(qr, kr, v.transpose(1, 2), 1 / math.sqrt(D), w, documents_idx_BxT=docs)
+    sps_b200.check_device_status()
+    assert torch.equal(out, out2)                      # bf16 v is read straight from the fused buffer
+    q_ref = orc.rope_cast(q.cpu(), fc.cpu()).transpose(1, 2)
+    k_ref = orc.rope_cast(k.cpu(), fc.cpu()).transpose(1, 2)
+    _ulp_close(qr, q_ref)
+    ref = orc.prefill_attention(qr.cpu(), kr.cpu(), vr.cpu(), 1 / math.sqrt(D), temporary_window=w, docs=docs.cpu())
+    _check(out, ref)

@@ -161,3 +161,17 @@ def test_cache_fill_matches_reference_handover(golden, tag):
     for name, val in (("br_k", br_k), ("br_v", br_v), ("br_len", br_len), ("nw_k", nw_k), ("nw_v", nw_v),
                       ("nw_len", nw_len), ("nw_pos", nw_pos)):
         assert np.array_equal(val.numpy(), g[name]), name
+
+
+@pytest.mark.parametrize("tag,dt", [("f32", torch.float32), ("bf16", torch.bfloat16)])
+def test_rope_cast_matches_reference_rotary(golden, tag, dt):
+    g = golden
+    fc = torch.view_as_complex(T(g["rope_freqs"]).contiguous())
+    pos = T(g["rope_pos"])
+    xq, xk = T(g[f"rope_{tag}_xq"]).to(dt), T(g[f"rope_{tag}_xk"]).to(dt)
+    for name, x, freqs in (("q1", xq, fc[pos]), ("k1", xk, fc[pos]),
+                           ("q2", xq, torch.stack([fc[pos], fc[pos + 7]])),
+                           ("k2", xk, torch.stack([fc[pos], fc[pos + 7]]))):
+        out = orc.rope_cast(x, freqs)
+        assert np.array_equal(out.float().numpy(), g[f"rope_{tag}_{name}"]), name
+    assert torch.equal(orc.rope_cast(xq, None), xq.to(torch.bfloat16))
