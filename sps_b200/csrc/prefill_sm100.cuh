@@ -480,16 +480,23 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           m_run = m_new;
         }
         const float neg_mc = -m_run * c;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        // packed fp32x2 arithmetic (sm_100): one FFMA2 scales and offsets two scores, one FADD2
+        // accumulates two probabilities; the exponentials stay one MUFU each
+        const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_mc, neg_mc);
+        float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
         uint32_t pk[kTileN / 2];
 #pragma unroll
-        for (int e = 0; e < kTileN; e += 2) {
-          const float p0 = fast_exp2(fmaf(s[e], c, neg_mc));
-          const float p1 = fast_exp2(fmaf(s[e + 1], c, neg_mc));
-          sum4[(e / 2) & 3] += p0 + p1;
-          pk[e / 2] = pack2<FP16>(p0, p1);
+        for (int e = 0; e < kTileN; e += 4) {
+          const float2 xa = __ffma2_rn(make_float2(s[e], s[e + 1]), c2, nm2);
+          const float2 xb = __ffma2_rn(make_float2(s[e + 2], s[e + 3]), c2, nm2);
+          const float2 pa = make_float2(fast_exp2(xa.x), fast_exp2(xa.y));
+          const float2 pb = make_float2(fast_exp2(xb.x), fast_exp2(xb.y));
+          sum_a = __fadd2_rn(sum_a, pa);
+          sum_b = __fadd2_rn(sum_b, pb);
+          pk[e / 2] = pack2<FP16>(pa.x, pa.y);
+          pk[e / 2 + 1] = pack2<FP16>(pb.x, pb.y);
         }
-        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        l_run += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         if (tid == 0) SPS_TRACE(j, 4);
 
         if (j > 0) {  // P buffer free and O stable once the previous P V product is done
