@@ -29,7 +29,9 @@ import os
 import sys
 
 sys.dont_write_bytecode = True
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF:
+    raise SystemExit("set REFERENCE_ROOT to the checkout of the reference project")
 sys.path[:0] = [os.path.join(REF, "src"), REF]
 
 import numpy as np
