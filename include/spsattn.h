@@ -21,7 +21,12 @@
  *   spsattn_decode_fwd       src/modeling/models/utils/decode_attention.py:483-594 (q=2), :393-480 (q=1)
  *   spsattn_kv_update        src/modeling/models/utils/decode_attention_fast.py:139-221
  *   spsattn_fill_decode_caches  src/modeling/models/reverse_sps/inference.py:568-613
- *   spsattn_rope_cast        src/modeling/models/model.py:201-230 + sps/core.py:53-55
+ *   spsattn_rope_cast, spsattn_qkv_rope_cast
+ *                            src/modeling/models/model.py:201-230 + sps/core.py:45-55
+ *   spsattn_decode_step      one layer of src/modeling/models/reverse_sps/inference.py:322-362 (attention)
+ *                            + :169-238 (cache update) in two launches
+ *   spsattn_add_rmsnorm, spsattn_swiglu
+ *                            src/modeling/models/model.py:101-132, :304-314, :324-327
  */
 #ifndef SPSATTN_H_
 #define SPSATTN_H_
@@ -35,6 +40,7 @@ extern "C" {
 
 #define SPSATTN_DTYPE_BF16 0
 #define SPSATTN_DTYPE_FP16 1
+#define SPSATTN_DTYPE_FP32 2   /* accepted only where an entry point says so */
 
 /* which key parity of the doubled sequence is persistent (window-exempt) */
 #define SPSATTN_PARITY_EVEN 0   /* SPS: input token slot            (triton_sps_flash_attention.py:97) */
@@ -186,6 +192,51 @@ int spsattn_decode_fwd_noalloc(const void* q, int nq, float* out,
                                int* device_status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * One layer of an SPS-family decode step: the segmented attention of spsattn_decode_fwd with the
+ * cache update of spsattn_kv_update folded into its merge pass, and the output written in the
+ * type the output projection consumes.  Stands in for the pair of calls the reference makes per
+ * layer and token (reverse_sps/inference.py:434-477: _attend_pair_from_decode_state, then
+ * _update_normal_memory + _update_predict_memory -> fused_sps_kv_update).
+ *
+ * `append` (NULL = attention only) names the ring and the retained cache of this layer, which
+ * must be the buffers the segments read, and this step's K/V rows for them.  The attention sees
+ * the caches as they are before the update; afterwards, for every active sequence, the rows are
+ * stored and the counters advanced exactly as spsattn_kv_update does.  All cache reads happen in
+ * the first launch and the counters are snapshotted there, the stores happen in the second.
+ * out_dtype: SPSATTN_DTYPE_FP32, or the queries' 16-bit type.  Workspace:
+ * spsattn_decode_step_workspace_bytes.  16-bit caches only.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct spsattn_kv_append {
+  void* nw_k;               /* device ring      [S, H, window_storage, D] */
+  void* nw_v;
+  int64_t* nw_len;          /* device [S] */
+  int64_t* nw_pos;          /* device [S] */
+  void* br_k;               /* device retained  [S, H, retained_storage, D] */
+  void* br_v;
+  int64_t* br_len;          /* device [S, H] */
+  const void* k_window;     /* device [S, H, D]: this step's row for the ring */
+  const void* v_window;
+  const void* k_retained;   /* device [S, H, D]: this step's row for the retained cache */
+  const void* v_retained;
+  const int8_t* active;     /* device [S] */
+  int32_t window_storage;
+  int32_t retained_storage;
+  int32_t window_tokens;    /* <= 0: no ring (ring pointers may be NULL) */
+  int32_t reserved;
+} spsattn_kv_append;
+
+size_t spsattn_decode_step_workspace_bytes(int S, int H, int D, int nq, const spsattn_segment* segs,
+                                           int n_segments);
+
+int spsattn_decode_step(const void* q, int nq, void* out, int out_dtype,
+                        const spsattn_segment* segs, int n_segments,
+                        const spsattn_extra* extras, int n_extras,
+                        const spsattn_kv_append* append_or_null,
+                        int S, int H, int D, int dtype, float sm_scale,
+                        void* workspace, size_t workspace_bytes,
+                        int* device_status, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Decode KV-cache update, in place (decode_attention_fast.py:34-136): for every active sequence
  * insert k_window/v_window into the ring [S,H,window_storage,D] at `pos` when the ring is full
  * (len >= window_tokens) else at `len`, then pos = (pos+1) % window_tokens or len += 1; append
@@ -215,6 +266,41 @@ int spsattn_rope_cast(const void* x, int x_dtype, int64_t x_stride_b, int64_t x_
                       int64_t x_stride_h, const float* freqs_cis, int64_t freqs_stride_b,
                       void* out, int out_dtype, int64_t out_stride_b, int64_t out_stride_n,
                       int64_t out_stride_h, int B, int N, int H, int D, int rotate, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * The same for a fused q/k/v projection in one launch (sps/core.py:45-55 splits c_attn's output
+ * into thirds, rotates q and k, casts all three).  x: [B, N, n_groups * heads_per_group, D] view;
+ * the heads are split into n_groups (1..3) consecutive groups and group g is written to
+ * groups[g].out with its own strides, rotated when groups[g].rotate is set, cast otherwise.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct spsattn_rope_group {
+  void* out;           /* device, 16-bit rows */
+  int64_t stride_b;    /* elements */
+  int64_t stride_n;
+  int64_t stride_h;
+  int32_t rotate;
+  int32_t reserved;
+} spsattn_rope_group;
+
+int spsattn_qkv_rope_cast(const void* x, int x_dtype, int64_t x_stride_b, int64_t x_stride_n,
+                          int64_t x_stride_h, const float* freqs_cis, int64_t freqs_stride_b,
+                          const spsattn_rope_group* groups, int n_groups, int out_dtype,
+                          int B, int N, int heads_per_group, int D, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * The element-wise passes of a decoder block around the attention call, so that a generation
+ * step is a fixed chain of launches (model.py:101-132 RMSNorm, :324-327 residual adds, :304-314
+ * SwiGLU MLP).  dtype: SPSATTN_DTYPE_BF16 (every intermediate rounded to bf16 where the
+ * reference's bf16 tensors round) or SPSATTN_DTYPE_FP32.
+ *
+ * spsattn_add_rmsnorm: x [rows, C] += delta (when delta is not NULL; x is updated in place),
+ * then y = cast(x_f32 * rsqrt(mean(x_f32^2) + eps)) * weight (when y is not NULL).
+ * spsattn_swiglu: y [rows, I] = silu(gate_up[:, :I]) * gate_up[:, I:], gate_up [rows, 2I].
+ * ------------------------------------------------------------------------------------------- */
+int spsattn_add_rmsnorm(void* x, const void* delta_or_null, const void* weight, void* y_or_null,
+                        int dtype, long long rows, int C, float eps, void* stream);
+
+int spsattn_swiglu(const void* gate_up, void* y, int dtype, long long rows, int I, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Prefill -> decode hand-over for one layer (src/modeling/models/reverse_sps/inference.py:568-613,

@@ -12,7 +12,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libspsattn.so")
 
-DTYPE_BF16, DTYPE_FP16 = 0, 1
+DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
 PARITY_EVEN, PARITY_ODD, PARITY_NONE = 0, 1, -1
 NO_WINDOW = -2147483648
 NOALLOC_SCRATCH_BYTES = 16 << 20
@@ -23,6 +23,8 @@ EXPORTS = (
     "spsattn_prefill_workspace_bytes", "spsattn_prefill_fwd", "spsattn_prefill_fwd_strided",
     "spsattn_decode_workspace_bytes", "spsattn_decode_fwd", "spsattn_decode_fwd_noalloc",
     "spsattn_kv_update", "spsattn_fill_decode_caches", "spsattn_rope_cast", "spsattn_debug_visibility",
+    "spsattn_decode_step_workspace_bytes", "spsattn_decode_step", "spsattn_qkv_rope_cast",
+    "spsattn_add_rmsnorm", "spsattn_swiglu",
 )
 
 
@@ -40,6 +42,24 @@ class Extra(C.Structure):
     """struct spsattn_extra"""
     _fields_ = [("k", C.c_void_p), ("v", C.c_void_p), ("query_mask", C.c_uint32),
                 ("reserved", C.c_uint32)]
+
+
+class KvAppend(C.Structure):
+    """struct spsattn_kv_append"""
+    _fields_ = [
+        ("nw_k", C.c_void_p), ("nw_v", C.c_void_p), ("nw_len", C.c_void_p), ("nw_pos", C.c_void_p),
+        ("br_k", C.c_void_p), ("br_v", C.c_void_p), ("br_len", C.c_void_p),
+        ("k_window", C.c_void_p), ("v_window", C.c_void_p),
+        ("k_retained", C.c_void_p), ("v_retained", C.c_void_p), ("active", C.c_void_p),
+        ("window_storage", C.c_int32), ("retained_storage", C.c_int32),
+        ("window_tokens", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
+class RopeGroup(C.Structure):
+    """struct spsattn_rope_group"""
+    _fields_ = [("out", C.c_void_p), ("stride_b", C.c_int64), ("stride_n", C.c_int64),
+                ("stride_h", C.c_int64), ("rotate", C.c_int32), ("reserved", C.c_int32)]
 
 
 class SpsAttnError(RuntimeError):
@@ -88,6 +108,18 @@ def load() -> C.CDLL:
     lib.spsattn_rope_cast.restype = i32
     lib.spsattn_rope_cast.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, i32, i64, i64, i64,
                                       i32, i32, i32, i32, i32, vp]
+    lib.spsattn_decode_step_workspace_bytes.restype = sz
+    lib.spsattn_decode_step_workspace_bytes.argtypes = [i32, i32, i32, i32, C.POINTER(Segment), i32]
+    lib.spsattn_decode_step.restype = i32
+    lib.spsattn_decode_step.argtypes = [vp, i32, vp, i32, C.POINTER(Segment), i32, C.POINTER(Extra), i32,
+                                        C.POINTER(KvAppend), i32, i32, i32, i32, f32, vp, sz, vp, vp]
+    lib.spsattn_qkv_rope_cast.restype = i32
+    lib.spsattn_qkv_rope_cast.argtypes = [vp, i32, i64, i64, i64, vp, i64, C.POINTER(RopeGroup), i32, i32,
+                                          i32, i32, i32, i32, vp]
+    lib.spsattn_add_rmsnorm.restype = i32
+    lib.spsattn_add_rmsnorm.argtypes = [vp, vp, vp, vp, i32, C.c_longlong, i32, f32, vp]
+    lib.spsattn_swiglu.restype = i32
+    lib.spsattn_swiglu.argtypes = [vp, vp, i32, C.c_longlong, i32, vp]
     lib.spsattn_debug_visibility.restype = i32
     lib.spsattn_debug_visibility.argtypes = [vp, vp, i32, i64, i64, i32, i32, i32, i32, i32, i32, vp, sz, vp]
     _lib = lib

@@ -17,7 +17,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libspsattn.so")
 SOURCES = ["spsattn_api.cu"]
 HEADERS = ["common.cuh", "mask.cuh", "prefill_sm100.cuh", "prefill_aux.cuh", "decode.cuh",
-           "kv_update.cuh", os.path.join("..", "..", "include", "spsattn.h")]
+           "kv_update.cuh", "model_glue.cuh", "rope.cuh", "cache_fill.cuh", os.path.join("..", "..", "include", "spsattn.h")]
 
 
 def _nvcc() -> str:

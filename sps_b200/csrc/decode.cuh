@@ -7,9 +7,15 @@
 // 128-bit loads (D/8 lanes per row, four row batches in flight per lane), keeps an online
 // softmax per lane group in fp32, merges the groups and writes one (max, sum, acc[D]) record
 // per query into the workspace; a second small kernel merges the records of each
-// (sequence, head) and writes fp32 output.  Lengths are read on the device, so the grid is
-// sized from the host-side caps and blocks past the live length return at once.
-// Reference computation: src/modeling/models/utils/decode_attention.py:191-368.
+// (sequence, head) and writes the output (fp32, or 16-bit for a caller that feeds a projection).
+// Lengths are read on the device, so the grid is sized from the host-side caps and blocks past
+// the live length return at once.
+// Optionally the merge kernel also performs the decode step's cache update (ring insert, retained
+// append, counters) for its (sequence, head): every read of the caches happened in the split
+// kernel, which has finished, and the counters the merge needs were snapshotted there, so no
+// block of the merge kernel reads a counter another block writes.
+// Reference computation: src/modeling/models/utils/decode_attention.py:191-368 and, for the
+// update, src/modeling/models/utils/decode_attention_fast.py:34-136.
 #pragma once
 
 #include "common.cuh"
@@ -32,10 +38,30 @@ struct DecodeSeg {
   uint32_t query_mask;
 };
 
+// The cache update folded into the merge kernel (all pointers null = no update).
+struct DecodeAppend {
+  uint16_t* nw_k;            // ring      [S, H, window_storage, D]
+  uint16_t* nw_v;
+  int64_t* nw_len;           // [S]
+  int64_t* nw_pos;           // [S]
+  uint16_t* br_k;            // retained  [S, H, retained_storage, D]
+  uint16_t* br_v;
+  int64_t* br_len;           // [S, H]
+  const uint16_t* k_window;  // [S, H, D]
+  const uint16_t* v_window;
+  const uint16_t* k_retained;
+  const uint16_t* v_retained;
+  const int8_t* active;      // [S]
+  int window_storage, retained_storage, window_tokens;
+};
+
 struct DecodeParams {
   const void* q;       // [S, nq, H, D]
-  float* out;          // [S, nq, H, D]
+  void* out;           // [S, nq, H, D] fp32, or 16-bit in the queries' format when out16 is set
+  int out16;
   float* partial;      // [S*H][n_chunks][nq][D + 2]
+  int4* snap;          // [S*H] (live rows, ring insert row, ring length, retained length) or null
+  DecodeAppend app;
   DecodeSeg seg[kMaxSegments];
   const void* extra_k[kMaxExtras];
   const void* extra_v[kMaxExtras];
@@ -74,6 +100,20 @@ decode_split_kernel(const DecodeParams prm) {
   for (int x = 0; x < kMaxSegments; ++x)
     seg_start[x + 1] = seg_start[x] + (x < prm.n_segments ? live_rows(prm.seg[x], s, h, prm.H) : 0);
   const int n_total = seg_start[kMaxSegments];
+  if (prm.snap != nullptr && chunk == 0 && tid == 0) {
+    // the counters as they are before this step's update; the merge kernel reads only these
+    long long ring_len = 0, ring_pos = 0, ret_len = 0;
+    if (prm.app.br_len != nullptr) ret_len = prm.app.br_len[(size_t)s * prm.H + h];
+    if (prm.app.window_tokens > 0) {
+      ring_len = prm.app.nw_len[s];
+      ring_pos = prm.app.nw_pos[s];
+    }
+    const long long ins = ring_len >= prm.app.window_tokens ? ring_pos : ring_len;
+    const long long big = 0x7fffffffLL;
+    prm.snap[sh] = make_int4(n_total, (int)(ins < 0 ? -1 : (ins > big ? big : ins)),
+                             (int)(ring_len > big ? big : ring_len),
+                             (int)(ret_len < 0 ? -1 : (ret_len > big ? big : ret_len)));
+  }
   const int c_lo = chunk * prm.chunk_rows;
   if (chunk > 0 && c_lo >= n_total) return;
   const int c_hi = min(c_lo + prm.chunk_rows, n_total);
@@ -243,29 +283,65 @@ decode_split_kernel(const DecodeParams prm) {
   }
 }
 
-// One block of D threads per (sequence, head, query): merge the chunk records.
-template <int D, int NQ>
+// One block of D threads per (sequence, head): merge the chunk records of each query, then
+// (when asked) store this step's K/V rows into the caches and advance the counters.
+template <int D, int NQ, bool FP16>
 __global__ void __launch_bounds__(D)
 decode_merge_kernel(const DecodeParams prm) {
   const int sh = blockIdx.x;
-  const int qi = blockIdx.y;
   const int s = sh / prm.H, h = sh % prm.H;
   const int d = threadIdx.x;
+  int4 snap = make_int4(0, 0, 0, 0);
   int n_total = 0;
-  for (int x = 0; x < prm.n_segments; ++x) n_total += live_rows(prm.seg[x], s, h, prm.H);
+  if (prm.snap != nullptr) {
+    snap = prm.snap[sh];
+    n_total = snap.x;
+  } else {
+    for (int x = 0; x < prm.n_segments; ++x) n_total += live_rows(prm.seg[x], s, h, prm.H);
+  }
   int n_chunks = (n_total + prm.chunk_rows - 1) / prm.chunk_rows;
   if (n_chunks < 1) n_chunks = 1;
-  const float* rec0 = prm.partial + (size_t)sh * prm.n_chunks * NQ * (D + 2) + qi * (D + 2);
-  float mx = -1.0e30f;
-  for (int c = 0; c < n_chunks; ++c) mx = fmaxf(mx, rec0[(size_t)c * NQ * (D + 2)]);
-  float a = 0.f, l = 0.f;
-  for (int c = 0; c < n_chunks; ++c) {
-    const float* rec = rec0 + (size_t)c * NQ * (D + 2);
-    const float f = fast_exp2(rec[0] - mx);
-    l += rec[1] * f;
-    a += rec[2 + d] * f;
+#pragma unroll
+  for (int qi = 0; qi < NQ; ++qi) {
+    const float* rec0 = prm.partial + (size_t)sh * prm.n_chunks * NQ * (D + 2) + qi * (D + 2);
+    float mx = -1.0e30f;
+    for (int c = 0; c < n_chunks; ++c) mx = fmaxf(mx, rec0[(size_t)c * NQ * (D + 2)]);
+    float a = 0.f, l = 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+      const float* rec = rec0 + (size_t)c * NQ * (D + 2);
+      const float f = fast_exp2(rec[0] - mx);
+      l += rec[1] * f;
+      a += rec[2 + d] * f;
+    }
+    const float o = l > 0.f ? a / l : 0.f;
+    const size_t off = (((size_t)s * NQ + qi) * prm.H + h) * D + d;
+    if (prm.out16)
+      reinterpret_cast<uint16_t*>(prm.out)[off] = (uint16_t)(pack2<FP16>(o, 0.f) & 0xffffu);
+    else
+      reinterpret_cast<float*>(prm.out)[off] = o;
   }
-  prm.out[(((size_t)s * NQ + qi) * prm.H + h) * D + d] = l > 0.f ? a / l : 0.f;
+  const DecodeAppend& ap = prm.app;
+  if (ap.br_k == nullptr || ap.active[s] == 0) return;
+  const size_t src = (size_t)sh * D + d;
+  if (ap.window_tokens > 0 && snap.y >= 0 && snap.y < ap.window_storage) {
+    const size_t dst = ((size_t)sh * ap.window_storage + (size_t)snap.y) * D + d;
+    ap.nw_k[dst] = ap.k_window[src];
+    ap.nw_v[dst] = ap.v_window[src];
+  }
+  if (snap.w >= 0 && snap.w < ap.retained_storage) {
+    const size_t dst = ((size_t)sh * ap.retained_storage + (size_t)snap.w) * D + d;
+    ap.br_k[dst] = ap.k_retained[src];
+    ap.br_v[dst] = ap.v_retained[src];
+  }
+  if (d == 0) {
+    if (snap.w < ap.retained_storage) ap.br_len[sh] = (long long)snap.w + 1;
+    if (h == 0 && ap.window_tokens > 0) {
+      if (snap.z >= ap.window_tokens)
+        ap.nw_pos[s] = ((long long)snap.y + 1) % ap.window_tokens;
+      else
+        ap.nw_len[s] = (long long)snap.z + 1;
+    }
+  }
 }
 
 }  // namespace spsattn

@@ -2,6 +2,9 @@
 // projection left them ([B, N, H, D] view, bf16 / fp16 / fp32, any row strides), rotates adjacent
 // element pairs by the position's complex frequency in fp32 and writes 16-bit rows in the layout
 // the attention kernel reads in place.  With rotate = 0 it is a plain cast (for v).
+// The H heads of the view may be split into up to three consecutive groups (the q, k and v thirds
+// of a fused projection), each with its own destination, strides and rotate flag, so that one
+// launch produces all three operands.
 // Reference computation: src/modeling/models/model.py:201-230 (apply_rotary_emb: view pairs as
 // complex, multiply by freqs_cis, back to real, cast) followed by the bf16 cast of
 // src/modeling/models/sps/core.py:53-55.
@@ -11,17 +14,24 @@
 
 namespace spsattn {
 
+constexpr int kMaxRopeGroups = 3;
+
+struct RopeGroup {
+  uint16_t* out;
+  int64_t os_b, os_n, os_h;    // elements
+  int rotate;
+};
+
 struct RopeParams {
   const void* x;
   int x_dtype;                 // 0 bf16, 1 fp16, 2 fp32
   int64_t xs_b, xs_n, xs_h;    // elements
   const float2* freqs;         // [N, D/2] or [B, N, D/2] (cos, sin)
   int64_t fs_b;                // elements of float2 per batch row, 0 when shared
-  uint16_t* out;
+  RopeGroup group[kMaxRopeGroups];
+  int heads_per_group;         // H = n_groups * heads_per_group
   int out_fp16;
-  int64_t os_b, os_n, os_h;
   int B, N, H, D;
-  int rotate;
 };
 
 __global__ void __launch_bounds__(256) rope_cast_kernel(const RopeParams p) {
@@ -52,7 +62,11 @@ __global__ void __launch_bounds__(256) rope_cast_kernel(const RopeParams p) {
         unpack2<false>(u.z, f[4], f[5]); unpack2<false>(u.w, f[6], f[7]);
       }
     }
-    if (p.rotate) {
+    const int gi = h / p.heads_per_group;
+    RopeGroup grp = p.group[0];   // selected without indexing the parameter block dynamically
+    if (gi == 1) grp = p.group[1];
+    if (gi == 2) grp = p.group[2];
+    if (grp.rotate) {
       const float2* fr = p.freqs + (size_t)b * p.fs_b + (size_t)n * (p.D / 2) + x8 * 4;
       const float4 c01 = *reinterpret_cast<const float4*>(fr);
       const float4 c23 = *reinterpret_cast<const float4*>(fr + 2);
@@ -73,7 +87,9 @@ __global__ void __launch_bounds__(256) rope_cast_kernel(const RopeParams p) {
       o.x = pack2<false>(f[0], f[1]); o.y = pack2<false>(f[2], f[3]);
       o.z = pack2<false>(f[4], f[5]); o.w = pack2<false>(f[6], f[7]);
     }
-    *reinterpret_cast<uint4*>(p.out + (size_t)b * p.os_b + (size_t)n * p.os_n + (size_t)h * p.os_h + x8 * 8) = o;
+    const int hg = h - gi * p.heads_per_group;
+    *reinterpret_cast<uint4*>(grp.out + (size_t)b * grp.os_b + (size_t)n * grp.os_n +
+                              (size_t)hg * grp.os_h + x8 * 8) = o;
   }
 }
 

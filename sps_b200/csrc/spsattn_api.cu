@@ -12,6 +12,7 @@
 #include "cache_fill.cuh"
 #include "decode.cuh"
 #include "kv_update.cuh"
+#include "model_glue.cuh"
 #include "prefill_aux.cuh"
 #include "prefill_sm100.cuh"
 #include "rope.cuh"
@@ -164,8 +165,7 @@ static int launch_decode(const DecodeParams& prm, cudaStream_t st) {
   decode_split_kernel<D, NQ, FP16><<<grid, kDecodeThreads, 0, st>>>(prm);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  dim3 mgrid((unsigned)(prm.S * prm.H), NQ);
-  decode_merge_kernel<D, NQ><<<mgrid, D, 0, st>>>(prm);
+  decode_merge_kernel<D, NQ, FP16><<<(unsigned)(prm.S * prm.H), D, 0, st>>>(prm);
   return (int)cudaGetLastError();
 }
 
@@ -330,9 +330,8 @@ int spsattn_debug_visibility(uint8_t* vis, const void* doc_ids, int doc_is_i64, 
 
 // ------------------------------------------------------------------------------------------ decode
 
-size_t spsattn_decode_workspace_bytes(int S, int H, int D, int nq, const spsattn_segment* segs,
-                                      int n_segments) {
-  if (S <= 0 || H <= 0 || D <= 0 || nq <= 0 || n_segments < 0 || (n_segments > 0 && !segs)) return 256;
+static size_t decode_records_bytes(int S, int H, int D, int nq, const spsattn_segment* segs,
+                                   int n_segments) {
   const long long rows = decode_max_rows(segs, n_segments);
   const int chunk = decode_chunk_rows(S, H, rows);
   long long n_chunks = (rows + chunk - 1) / chunk;
@@ -340,17 +339,30 @@ size_t spsattn_decode_workspace_bytes(int S, int H, int D, int nq, const spsattn
   return align_up((size_t)S * H * n_chunks * nq * (D + 2) * sizeof(float), 256);
 }
 
-int spsattn_decode_fwd(const void* q, int nq, float* out, const spsattn_segment* segs, int n_segments,
-                       const spsattn_extra* extras, int n_extras, int S, int H, int D, int dtype,
-                       float sm_scale, void* workspace, size_t workspace_bytes, int* device_status,
-                       void* stream) {
-  (void)device_status;
+size_t spsattn_decode_workspace_bytes(int S, int H, int D, int nq, const spsattn_segment* segs,
+                                      int n_segments) {
+  if (S <= 0 || H <= 0 || D <= 0 || nq <= 0 || n_segments < 0 || (n_segments > 0 && !segs)) return 256;
+  return decode_records_bytes(S, H, D, nq, segs, n_segments);
+}
+
+size_t spsattn_decode_step_workspace_bytes(int S, int H, int D, int nq, const spsattn_segment* segs,
+                                           int n_segments) {
+  if (S <= 0 || H <= 0 || D <= 0 || nq <= 0 || n_segments < 0 || (n_segments > 0 && !segs)) return 256;
+  return decode_records_bytes(S, H, D, nq, segs, n_segments) + align_up((size_t)S * H * sizeof(int4), 256);
+}
+
+// Shared body of the decode entry points.  out_dtype: 2 = fp32, else 16-bit in the queries' format.
+static int decode_impl(const void* q, int nq, void* out, int out_dtype, const spsattn_segment* segs,
+                       int n_segments, const spsattn_extra* extras, int n_extras,
+                       const spsattn_kv_append* append, int S, int H, int D, int dtype, float sm_scale,
+                       void* workspace, size_t workspace_bytes, void* stream) {
   if (!q || !out) return SPSATTN_ERR_ARG;
   if (nq != 1 && nq != 2) return SPSATTN_ERR_ARG;
   if (S <= 0 || H <= 0) return SPSATTN_ERR_ARG;
   if (n_segments < 0 || n_segments > kMaxSegments || (n_segments > 0 && !segs)) return SPSATTN_ERR_ARG;
   if (n_extras < 0 || n_extras > kMaxExtras || (n_extras > 0 && !extras)) return SPSATTN_ERR_ARG;
   if (dtype != SPSATTN_DTYPE_BF16 && dtype != SPSATTN_DTYPE_FP16) return SPSATTN_ERR_ARG;
+  if (out_dtype != SPSATTN_DTYPE_FP32 && out_dtype != dtype) return SPSATTN_ERR_ARG;
   if (!isfinite(sm_scale)) return SPSATTN_ERR_ARG;
   if (D != 8 && D != 16 && D != 32 && D != 64 && D != 128 && D != 256) return SPSATTN_ERR_HEAD_DIM;
   if (!aligned16(q) || !aligned16(out)) return SPSATTN_ERR_ALIGN;
@@ -390,11 +402,42 @@ int spsattn_decode_fwd(const void* q, int nq, float* out, const spsattn_segment*
   if (n_chunks < 1) n_chunks = 1;
   if (n_chunks > 65535) return SPSATTN_ERR_TOO_LARGE;
   prm.n_chunks = (int)n_chunks;
-  const size_t need = (size_t)S * H * n_chunks * nq * (D + 2) * sizeof(float);
+  const size_t raw = (size_t)S * H * n_chunks * nq * (D + 2) * sizeof(float);
+  const size_t records = align_up(raw, 256);
+  const size_t need = append ? records + (size_t)S * H * sizeof(int4) : raw;
   if (!workspace || workspace_bytes < need) return SPSATTN_ERR_WORKSPACE;
   if (!aligned16(workspace)) return SPSATTN_ERR_ALIGN;
+  if (append) {
+    const spsattn_kv_append& a = *append;
+    if (!a.br_k || !a.br_v || !a.br_len || !a.k_retained || !a.v_retained || !a.active)
+      return SPSATTN_ERR_ARG;
+    if (a.retained_storage < 0) return SPSATTN_ERR_ARG;
+    if (a.window_tokens > 0) {
+      if (!a.nw_k || !a.nw_v || !a.nw_len || !a.nw_pos || !a.k_window || !a.v_window)
+        return SPSATTN_ERR_ARG;
+      if (a.window_storage <= 0) return SPSATTN_ERR_ARG;
+    }
+    DecodeAppend& d = prm.app;
+    d.nw_k = reinterpret_cast<uint16_t*>(a.nw_k);
+    d.nw_v = reinterpret_cast<uint16_t*>(a.nw_v);
+    d.nw_len = a.nw_len;
+    d.nw_pos = a.nw_pos;
+    d.br_k = reinterpret_cast<uint16_t*>(a.br_k);
+    d.br_v = reinterpret_cast<uint16_t*>(a.br_v);
+    d.br_len = a.br_len;
+    d.k_window = reinterpret_cast<const uint16_t*>(a.k_window);
+    d.v_window = reinterpret_cast<const uint16_t*>(a.v_window);
+    d.k_retained = reinterpret_cast<const uint16_t*>(a.k_retained);
+    d.v_retained = reinterpret_cast<const uint16_t*>(a.v_retained);
+    d.active = a.active;
+    d.window_storage = a.window_storage;
+    d.retained_storage = a.retained_storage;
+    d.window_tokens = a.window_tokens > 0 ? a.window_tokens : 0;
+    prm.snap = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(workspace) + records);
+  }
   prm.q = q;
   prm.out = out;
+  prm.out16 = out_dtype != SPSATTN_DTYPE_FP32;
   prm.partial = reinterpret_cast<float*>(workspace);
   prm.n_segments = n_segments;
   prm.n_extras = n_extras;
@@ -414,45 +457,95 @@ int spsattn_decode_fwd(const void* q, int nq, float* out, const spsattn_segment*
   }
 }
 
+int spsattn_decode_fwd(const void* q, int nq, float* out, const spsattn_segment* segs, int n_segments,
+                       const spsattn_extra* extras, int n_extras, int S, int H, int D, int dtype,
+                       float sm_scale, void* workspace, size_t workspace_bytes, int* device_status,
+                       void* stream) {
+  (void)device_status;
+  return decode_impl(q, nq, out, SPSATTN_DTYPE_FP32, segs, n_segments, extras, n_extras, nullptr, S, H, D,
+                     dtype, sm_scale, workspace, workspace_bytes, stream);
+}
+
+int spsattn_decode_step(const void* q, int nq, void* out, int out_dtype, const spsattn_segment* segs,
+                        int n_segments, const spsattn_extra* extras, int n_extras,
+                        const spsattn_kv_append* append, int S, int H, int D, int dtype, float sm_scale,
+                        void* workspace, size_t workspace_bytes, int* device_status, void* stream) {
+  (void)device_status;
+  return decode_impl(q, nq, out, out_dtype, segs, n_segments, extras, n_extras, append, S, H, D, dtype,
+                     sm_scale, workspace, workspace_bytes, stream);
+}
+
 // ------------------------------------------------------------------------------------ rope + cast
+
+static int rope_impl(const void* x, int x_dtype, int64_t xs_b, int64_t xs_n, int64_t xs_h,
+                     const float* freqs_cis, int64_t freqs_stride_b, const spsattn_rope_group* groups,
+                     int n_groups, int out_dtype, int B, int N, int heads_per_group, int D, void* stream) {
+  if (!x || !groups || n_groups < 1 || n_groups > kMaxRopeGroups) return SPSATTN_ERR_ARG;
+  if (B <= 0 || N <= 0 || heads_per_group <= 0 || D <= 0) return SPSATTN_ERR_ARG;
+  if (x_dtype < 0 || x_dtype > 2) return SPSATTN_ERR_ARG;
+  if (out_dtype != SPSATTN_DTYPE_BF16 && out_dtype != SPSATTN_DTYPE_FP16) return SPSATTN_ERR_ARG;
+  if (D % 8) return SPSATTN_ERR_HEAD_DIM;
+  const int in_align = x_dtype == 2 ? 4 : 8;   // elements per 16 bytes
+  if ((xs_b % in_align) || (xs_n % in_align) || (xs_h % in_align) || (freqs_stride_b % 2))
+    return SPSATTN_ERR_ALIGN;
+  if (!aligned16(x)) return SPSATTN_ERR_ALIGN;
+  RopeParams p;
+  memset(&p, 0, sizeof(p));
+  bool any_rotate = false;
+  for (int g = 0; g < n_groups; ++g) {
+    const spsattn_rope_group& sg = groups[g];
+    if (!sg.out) return SPSATTN_ERR_ARG;
+    if ((sg.stride_b % 8) || (sg.stride_n % 8) || (sg.stride_h % 8) || !aligned16(sg.out))
+      return SPSATTN_ERR_ALIGN;
+    p.group[g].out = reinterpret_cast<uint16_t*>(sg.out);
+    p.group[g].os_b = sg.stride_b;
+    p.group[g].os_n = sg.stride_n;
+    p.group[g].os_h = sg.stride_h;
+    p.group[g].rotate = sg.rotate != 0;
+    any_rotate |= sg.rotate != 0;
+  }
+  if (any_rotate && (!freqs_cis || !aligned16(freqs_cis))) return freqs_cis ? SPSATTN_ERR_ALIGN : SPSATTN_ERR_ARG;
+  p.x = x;
+  p.x_dtype = x_dtype;
+  p.xs_b = xs_b;
+  p.xs_n = xs_n;
+  p.xs_h = xs_h;
+  p.freqs = reinterpret_cast<const float2*>(freqs_cis);
+  p.fs_b = freqs_stride_b;
+  p.heads_per_group = heads_per_group;
+  p.out_fp16 = out_dtype == SPSATTN_DTYPE_FP16;
+  p.B = B;
+  p.N = N;
+  p.H = heads_per_group * n_groups;
+  p.D = D;
+  const long long total = (long long)B * N * p.H * (D / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  rope_cast_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return (int)cudaGetLastError();
+}
 
 int spsattn_rope_cast(const void* x, int x_dtype, int64_t x_stride_b, int64_t x_stride_n,
                       int64_t x_stride_h, const float* freqs_cis, int64_t freqs_stride_b, void* out,
                       int out_dtype, int64_t out_stride_b, int64_t out_stride_n, int64_t out_stride_h,
                       int B, int N, int H, int D, int rotate, void* stream) {
-  if (!x || !out || (rotate && !freqs_cis)) return SPSATTN_ERR_ARG;
-  if (B <= 0 || N <= 0 || H <= 0 || D <= 0) return SPSATTN_ERR_ARG;
-  if (x_dtype < 0 || x_dtype > 2) return SPSATTN_ERR_ARG;
-  if (out_dtype != SPSATTN_DTYPE_BF16 && out_dtype != SPSATTN_DTYPE_FP16) return SPSATTN_ERR_ARG;
-  if (D % 8) return SPSATTN_ERR_HEAD_DIM;
-  const int in_align = x_dtype == 2 ? 4 : 8;   // elements per 16 bytes
-  if ((x_stride_b % in_align) || (x_stride_n % in_align) || (x_stride_h % in_align) ||
-      (out_stride_b % 8) || (out_stride_n % 8) || (out_stride_h % 8) || (freqs_stride_b % 2))
-    return SPSATTN_ERR_ALIGN;
-  if (!aligned16(x) || !aligned16(out) || (rotate && !aligned16(freqs_cis))) return SPSATTN_ERR_ALIGN;
-  RopeParams p;
-  p.x = x;
-  p.x_dtype = x_dtype;
-  p.xs_b = x_stride_b;
-  p.xs_n = x_stride_n;
-  p.xs_h = x_stride_h;
-  p.freqs = reinterpret_cast<const float2*>(freqs_cis);
-  p.fs_b = freqs_stride_b;
-  p.out = reinterpret_cast<uint16_t*>(out);
-  p.out_fp16 = out_dtype == SPSATTN_DTYPE_FP16;
-  p.os_b = out_stride_b;
-  p.os_n = out_stride_n;
-  p.os_h = out_stride_h;
-  p.B = B;
-  p.N = N;
-  p.H = H;
-  p.D = D;
-  p.rotate = rotate;
-  const long long total = (long long)B * N * H * (D / 8);
-  long long blocks = (total + 255) / 256;
-  if (blocks > 148LL * 32) blocks = 148LL * 32;
-  rope_cast_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
-  return (int)cudaGetLastError();
+  spsattn_rope_group g;
+  g.out = out;
+  g.stride_b = out_stride_b;
+  g.stride_n = out_stride_n;
+  g.stride_h = out_stride_h;
+  g.rotate = rotate;
+  g.reserved = 0;
+  return rope_impl(x, x_dtype, x_stride_b, x_stride_n, x_stride_h, freqs_cis, freqs_stride_b, &g, 1,
+                   out_dtype, B, N, H, D, stream);
+}
+
+int spsattn_qkv_rope_cast(const void* x, int x_dtype, int64_t x_stride_b, int64_t x_stride_n,
+                          int64_t x_stride_h, const float* freqs_cis, int64_t freqs_stride_b,
+                          const spsattn_rope_group* groups, int n_groups, int out_dtype, int B, int N,
+                          int heads_per_group, int D, void* stream) {
+  return rope_impl(x, x_dtype, x_stride_b, x_stride_n, x_stride_h, freqs_cis, freqs_stride_b, groups,
+                   n_groups, out_dtype, B, N, heads_per_group, D, stream);
 }
 
 // ------------------------------------------------------------------------------- prefill -> caches
@@ -577,6 +670,57 @@ int spsattn_kv_update(void* nw_k, void* nw_v, int64_t* nw_len, int64_t* nw_pos, 
   p.retained_storage = retained_storage;
   p.window_tokens = window_tokens > 0 ? window_tokens : 0;
   kv_update_kernel<<<S, 256, (size_t)H * sizeof(long long), reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------ block glue (norm, gate)
+
+int spsattn_add_rmsnorm(void* x, const void* delta, const void* weight, void* y, int dtype,
+                        long long rows, int C, float eps, void* stream) {
+  if (!x || !weight || (!y && !delta)) return SPSATTN_ERR_ARG;
+  if (rows <= 0 || C <= 0 || !(eps >= 0.f)) return SPSATTN_ERR_ARG;
+  if (dtype != SPSATTN_DTYPE_BF16 && dtype != SPSATTN_DTYPE_FP32) return SPSATTN_ERR_ARG;
+  const int vec = dtype == SPSATTN_DTYPE_BF16 ? 8 : 4;
+  if (C % vec) return SPSATTN_ERR_ALIGN;
+  if (!aligned16(x) || !aligned16(weight) || (y && !aligned16(y)) || (delta && !aligned16(delta)))
+    return SPSATTN_ERR_ALIGN;
+  RmsNormParams p;
+  p.x = x;
+  p.delta = delta;
+  p.weight = weight;
+  p.y = y;
+  p.rows = rows;
+  p.C = C;
+  p.eps = eps;
+  const unsigned blocks = (unsigned)(rows < 148LL * 16 ? rows : 148LL * 16);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == SPSATTN_DTYPE_BF16)
+    add_rmsnorm_kernel<true><<<blocks, 256, 0, st>>>(p);
+  else
+    add_rmsnorm_kernel<false><<<blocks, 256, 0, st>>>(p);
+  return (int)cudaGetLastError();
+}
+
+int spsattn_swiglu(const void* gate_up, void* y, int dtype, long long rows, int I, void* stream) {
+  if (!gate_up || !y) return SPSATTN_ERR_ARG;
+  if (rows <= 0 || I <= 0) return SPSATTN_ERR_ARG;
+  if (dtype != SPSATTN_DTYPE_BF16 && dtype != SPSATTN_DTYPE_FP32) return SPSATTN_ERR_ARG;
+  const int vec = dtype == SPSATTN_DTYPE_BF16 ? 8 : 4;
+  if (I % vec) return SPSATTN_ERR_ALIGN;
+  if (!aligned16(gate_up) || !aligned16(y)) return SPSATTN_ERR_ALIGN;
+  SwigluParams p;
+  p.gate_up = gate_up;
+  p.y = y;
+  p.rows = rows;
+  p.I = I;
+  const long long total = rows * (I / vec);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == SPSATTN_DTYPE_BF16)
+    swiglu_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(p);
+  else
+    swiglu_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(p);
   return (int)cudaGetLastError();
 }
 

@@ -17,6 +17,10 @@ It imports, unmodified, from the reference:
     and the prefill -> decode hand-over     src/modeling/models/reverse_sps/inference.py:568-613
     through the reference's own tiny Delayed-State / SPS test models.
   * ``apply_rotary_emb``, ``precompute_freqs_cis``  src/modeling/models/model.py:134-230
+  * ``SPSModel`` / ``ReverseSPSModel`` themselves (src/modeling/models/sps/, reverse_sps/): dense
+    ``forward`` (its attention name rebound to the SDPA oracle above, since the Triton kernel needs
+    a GPU), stepwise ``forward_efficient`` (with the eager cache updates) and greedy tokens
+    obtained the way tests/models/sps/test_dense_only.py:212-249 obtains them.
 
 Every case stores its inputs (bf16/fp16 values widened to fp32, integer tensors
 as int64) next to the reference output so the tests need nothing but numpy.
@@ -280,6 +284,83 @@ def rope_cases():
     put("rope_pos", pos)
 
 
+def model_cases():
+    """Logits and greedy tokens of the reference's own tiny SPS and Reverse-SPS models on CPU fp32
+    (sizes of tests/models/sps/test_dense_only.py:13, head_dim 64), weights included."""
+    import types
+    import modeling.models.sps.core as sps_core
+    import modeling.models.reverse_sps.core as rsps_core
+    from modeling.models.reverse_sps import ReverseSPSConfig, ReverseSPSModel
+    from modeling.models.reverse_sps.inference import ReverseSPSInferenceMixin as Mixin
+    from modeling.models.sps import SPSConfig, SPSModel
+
+    def sps_attn(q, k, v, sm_scale, temporary_key_window, warp_specialize=True, documents_idx_BxT=None,
+                 persistent_key_window=None):
+        assert persistent_key_window is None
+        return _sdpa_reference_attention_sps(q.float(), k.float(), v.float(), temporary_key_window,
+                                             documents_idx_BxT)
+
+    def rsps_attn(q, k, v, sm_scale, temporary_key_window, warp_specialize=True, documents_idx_BxT=None,
+                  persistent_key_window=None):
+        # this oracle has no document argument: only single-document rows go through it
+        assert persistent_key_window is None
+        assert documents_idx_BxT is None or bool((documents_idx_BxT == documents_idx_BxT[:, :1]).all())
+        return _reference_persistent_key_window_attention(
+            q.float(), k.float(), v.float(), temporary_key_window=temporary_key_window,
+            persistent_key_window=2 * q.shape[2], persistent_key_remainder=1)
+
+    sps_core.triton_sps_sliding_attention = sps_attn
+    rsps_core.triton_reverse_sps_sliding_attention = rsps_attn
+    for tag, cfg_cls, model_cls, w in (("sps", SPSConfig, SPSModel, 2), ("sps_w5", SPSConfig, SPSModel, 5),
+                                       ("rsps", ReverseSPSConfig, ReverseSPSModel, 3)):
+        torch.manual_seed(41)
+        cfg = cfg_cls(block_size=32, vocab_size=64, n_layer=2, n_head=2, hidden_size=128,
+                      intermediate_size=256, dropout=0.0, bias=False, eos_token_id=63, pad_token_id=62,
+                      predict_token_id=61, window_size=w, enable_triton_attention=True,
+                      warp_specialize=False)
+        model = model_cls(cfg).eval()
+        # larger weights than the 0.02 init so that logits are not near-ties; bf16-representable
+        # so that a bf16 run starts from identical parameters
+        with torch.no_grad():
+            for prm in model.parameters():
+                if prm.dim() >= 2:
+                    prm.mul_(6.0)
+                prm.copy_(prm.bfloat16().float())
+        model._update_normal_memory = types.MethodType(Mixin._update_normal_memory_unfused, model)
+        model._update_predict_memory = types.MethodType(Mixin._update_predict_memory_unfused, model)
+        for name, t in model.state_dict().items():
+            put(f"model_{tag}_w__{name}", t)
+        put(f"model_{tag}_dims", np.array([cfg.block_size, cfg.vocab_size, cfg.n_layer, cfg.n_head,
+                                            cfg.hidden_size, cfg.intermediate_size, cfg.eos_token_id,
+                                            cfg.pad_token_id, cfg.predict_token_id, cfg.window_size]))
+        eos, pad = cfg.eos_token_id, cfg.pad_token_id
+        g = torch.Generator().manual_seed(43)
+        dense_idx = torch.randint(0, 60, (2, 12), generator=g)
+        if tag != "rsps":
+            dense_idx[1, 4] = eos
+        put(f"model_{tag}_dense_idx", dense_idx)
+        put(f"model_{tag}_dense_logits", model(dense_idx))
+        put(f"model_{tag}_stepwise_logits", model.forward_efficient(dense_idx))
+        padded = torch.randint(0, 60, (3, 10), generator=g)
+        padded[0, :3] = pad
+        padded[1, 5] = eos
+        padded[2, :6] = pad
+        padded[2, 7] = eos
+        put(f"model_{tag}_padded_idx", padded)
+        put(f"model_{tag}_padded_logits", model.forward_efficient(padded))
+        seq = padded.clone()
+        margins = []
+        for _ in range(8):
+            z = model.forward_efficient(seq)[:, -1, :].clone()
+            z[:, cfg.predict_token_id] = float("-inf")
+            z[:, cfg.pad_token_id] = float("-inf")
+            top2 = z.topk(2, dim=-1).values
+            margins.append(top2[:, 0] - top2[:, 1])
+            seq = torch.cat([seq, z.argmax(dim=-1, keepdim=True)], dim=1)
+        put(f"model_{tag}_greedy", seq)
+        OUT[f"model_{tag}_greedy_margin"] = torch.stack(margins, dim=1).numpy()
+
+
 if __name__ == "__main__":
     with torch.no_grad():
         sps_cases()
@@ -290,6 +371,7 @@ if __name__ == "__main__":
         kv_update_cases()
         cache_fill_cases()
         rope_cases()
+        model_cases()
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
     np.savez_compressed(path, **OUT)
     print(f"wrote {path}: {len(OUT)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
