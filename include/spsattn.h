@@ -270,8 +270,9 @@ int spsattn_rope_cast(const void* x, int x_dtype, int64_t x_stride_b, int64_t x_
 /* ---------------------------------------------------------------------------------------------
  * The same for a fused q/k/v projection in one launch (sps/core.py:45-55 splits c_attn's output
  * into thirds, rotates q and k, casts all three).  x: [B, N, n_groups * heads_per_group, D] view;
- * the heads are split into n_groups (1..3) consecutive groups and group g is written to
+ * the heads are split into n_groups (1..6) consecutive groups and group g is written to
  * groups[g].out with its own strides, rotated when groups[g].rotate is set, cast otherwise.
+ * (A decode step passes the [S, 2, 3C] projection of a token pair as N = 1 with six groups.)
  * ------------------------------------------------------------------------------------------- */
 typedef struct spsattn_rope_group {
   void* out;           /* device, 16-bit rows */

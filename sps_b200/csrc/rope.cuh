@@ -2,9 +2,9 @@
 // projection left them ([B, N, H, D] view, bf16 / fp16 / fp32, any row strides), rotates adjacent
 // element pairs by the position's complex frequency in fp32 and writes 16-bit rows in the layout
 // the attention kernel reads in place.  With rotate = 0 it is a plain cast (for v).
-// The H heads of the view may be split into up to three consecutive groups (the q, k and v thirds
-// of a fused projection), each with its own destination, strides and rotate flag, so that one
-// launch produces all three operands.
+// The H heads of the view may be split into up to six consecutive groups (the q, k and v thirds
+// of a fused projection; for a decode step, those of both slots of a token pair), each with its
+// own destination, strides and rotate flag, so that one launch produces all operands.
 // Reference computation: src/modeling/models/model.py:201-230 (apply_rotary_emb: view pairs as
 // complex, multiply by freqs_cis, back to real, cast) followed by the bf16 cast of
 // src/modeling/models/sps/core.py:53-55.
@@ -14,7 +14,7 @@
 
 namespace spsattn {
 
-constexpr int kMaxRopeGroups = 3;
+constexpr int kMaxRopeGroups = 6;
 
 struct RopeGroup {
   uint16_t* out;
@@ -66,6 +66,9 @@ __global__ void __launch_bounds__(256) rope_cast_kernel(const RopeParams p) {
     RopeGroup grp = p.group[0];   // selected without indexing the parameter block dynamically
     if (gi == 1) grp = p.group[1];
     if (gi == 2) grp = p.group[2];
+    if (gi == 3) grp = p.group[3];
+    if (gi == 4) grp = p.group[4];
+    if (gi == 5) grp = p.group[5];
     if (grp.rotate) {
       const float2* fr = p.freqs + (size_t)b * p.fs_b + (size_t)n * (p.D / 2) + x8 * 4;
       const float4 c01 = *reinterpret_cast<const float4*>(fr);
