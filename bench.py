@@ -34,6 +34,7 @@ if ROOT not in sys.path:
 PREFILL = "cfg1_s_scale"
 DECODE = "cfg2_segmented_decode"
 PREFILL_FULL_WINDOW = "cfg4_full_window"
+GENERATION = "cfg3_xl_generation"
 # DRAM traffic per full-size launch, from ncu captures of a smaller case scaled by the units
 # processed (traffic is proportional to batch rows / sequences)
 PREFILL_DRAM_BYTES_PER_LAUNCH = 2 * (151.4e6 + 34.0e6)
@@ -317,6 +318,12 @@ def run_ours(args):
         }
         sps_b200.check_device_status(device)
 
+    # ---------------- whole-model greedy generation with the attention path inside
+    if not args.skip_generation:
+        wl = out = dw = segs = None
+        torch.cuda.empty_cache()
+        result["generation"] = run_generation(GENERATION, world, rank, device, peaks, peak_kind)
+
     # ---------------- CPU baseline beside it (rank 0, single GPU runs only)
     if world == 1 and not args.skip_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(budget_s=12.0)
@@ -327,15 +334,96 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_generation(name, world, rank, device, peaks, peak_kind, new_tokens=None, runs_n=3):
+    """Prompt prefill + greedy decode of a random-init SPS decoder, data parallel over ranks
+    (the batch is split, weights replicated).  Tokens/s as the reference's speed benchmark
+    defines them: batch * new_tokens / (prefill + decode), and batch * (new_tokens - 1) / decode."""
+    import ctypes as C
+    import sps_b200
+    from sps_b200 import _lib, workloads
+    from sps_b200.generation import SPSDims, SPSGenerator, random_state_dict
+
+    cfg = workloads.GENERATION_CONFIGS[name]
+    dims = SPSDims(**{k: cfg[k] for k in ("block_size", "vocab_size", "n_layer", "n_head", "hidden_size",
+                                          "intermediate_size", "eos_token_id", "pad_token_id",
+                                          "predict_token_id", "window_size")})
+    batch = max(1, cfg["batch"] // world)
+    eng = SPSGenerator(random_state_dict(dims, seed=0, device=device), dims, variant="sps", device=device)
+    prompts = torch.from_numpy(workloads.generation_prompts(cfg, batch, seed=rank)).to(device)
+    forbidden = torch.tensor(workloads.generation_forbidden_ids(cfg))
+    new = int(new_tokens or cfg["new_tokens"])
+    eng.generate(prompts, new, stop_on_eos=False, forbidden_token_ids=forbidden)      # builds and captures
+    runs = []
+    for _ in range(runs_n):
+        torch.cuda.synchronize()
+        barrier(world)
+        tm = {}
+        eng.generate(prompts, new, stop_on_eos=False, forbidden_token_ids=forbidden, timings=tm)
+        runs.append(tm)
+    sps_b200.check_device_status(device)
+    tm = sorted(runs, key=lambda t: t["prefill"] + t["decode"])[len(runs) // 2]        # median run
+    total_ms = max_over_ranks(tm["prefill"] + tm["decode"], world, device)
+    decode_ms = max_over_ranks(tm["decode"], world, device)
+    prefill_ms = max_over_ranks(tm["prefill"], world, device)
+    step_ms = tm["decode_steps"] / tm["n_steps"]
+    # the attention launches of one token alone (24 x split + merge, no cache update)
+    s = eng._step
+    scale = 1.0 / (dims.head_dim ** 0.5)
+    lib = _lib.load()
+
+    def attention_only():
+        for segs, n_seg, extras, _ap in s.layer_args:
+            lib.spsattn_decode_step(s.q.data_ptr(), 2, s.y.data_ptr(), _lib.DTYPE_BF16, segs, n_seg, extras, 2,
+                                    None, batch, dims.n_head, dims.head_dim, _lib.DTYPE_BF16, scale,
+                                    s.ws.data_ptr(), s.ws_bytes, None,
+                                    torch.cuda.current_stream().cuda_stream)
+
+    for _ in range(3):
+        attention_only()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(10):
+        attention_only()
+    t1.record()
+    torch.cuda.synchronize()
+    attn_ms = t0.elapsed_time(t1) / 10
+    live = cfg["prompt"] + new / 2.0
+    step_bytes = workloads.generation_step_bytes(cfg, batch, live)
+    hbm = float(peaks["hbm_gbs"])
+    gbs = step_bytes / (step_ms * 1e-3) / 1e9
+    return {
+        "workload": f"{name}: SPS decoder {dims.n_layer} layers, hidden {dims.hidden_size}, {dims.n_head} heads x "
+                    f"{dims.head_dim}, SwiGLU {dims.intermediate_size}, vocabulary {dims.vocab_size}, bf16, random "
+                    f"init; batch {batch} per GPU ({batch * world} in all), prompt {cfg['prompt']}, {new} new "
+                    f"tokens, greedy, w={dims.window_size}",
+        "tokens_per_s": world * batch * new / (total_ms * 1e-3),
+        "decode_tokens_per_s": world * batch * (new - 1) / (decode_ms * 1e-3),
+        "prefill_ms": prefill_ms, "decode_ms": decode_ms, "ms_per_token_step": step_ms,
+        "attention_ms_per_token_step": attn_ms, "attention_share_of_step": attn_ms / step_ms,
+        "scaling": "strong (batch split over ranks, weights replicated)",
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                     "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
+                     "bytes_per_step": step_bytes,
+                     "note": "whole token step: every parameter once + live K/V of all layers at mid-generation"},
+    }
+
+
 def run_case(args):
     """Small single-kernel cases for profiler captures (a few hundred MB on the device, inputs
     still larger than L2): `prefill-small` = 4 of the 8 batch rows of the s-scale prefill,
-    `decode-small` = 32 of the 128 decode sequences.  Prints a short JSON line, not the
-    benchmark contract line."""
+    `decode-small` = 32 of the 128 decode sequences, `generation-small` / `generation` = the
+    whole-model generation leg alone on a tiny / the full model.  Prints a short JSON line, not
+    the benchmark contract line."""
     import sps_b200
     from sps_b200 import workloads
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
+    if args.case in ("generation-small", "generation"):
+        peaks, peak_kind = load_peaks()
+        name = "generation_small" if args.case == "generation-small" else GENERATION
+        print(json.dumps({"case": args.case, **run_generation(name, 1, 0, device, peaks, peak_kind,
+                                                              new_tokens=args.new_tokens, runs_n=args.runs)}))
+        return
     if args.case == "prefill-small":
         wl = workloads.make_prefill(PREFILL, device, batch_slice=slice(0, 4))
         out = torch.empty_like(wl.q)
@@ -439,11 +527,14 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--case", choices=["full", "prefill-small", "decode-small"], default="full")
+    ap.add_argument("--case", choices=["full", "prefill-small", "decode-small", "generation-small", "generation"], default="full")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-decode", action="store_true")
     ap.add_argument("--skip-full-window", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-generation", action="store_true")
+    ap.add_argument("--new-tokens", type=int, default=None, help="generation cases: tokens to generate")
+    ap.add_argument("--runs", type=int, default=3, help="generation cases: timed repetitions")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -186,8 +186,8 @@ class SPSGenerator:
         freqs = 1.0 / (10000.0 ** (torch.arange(0, hd, 2)[: hd // 2].float() / hd))
         ang = torch.outer(torch.arange(dims.block_size).float(), freqs)
         self.freqs = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(self.device).contiguous()
-        self._graph = None
         self._step = None
+        self._session = None
 
     # ------------------------------------------------------------------ library calls
     def _stream(self):
@@ -309,9 +309,10 @@ class SPSGenerator:
         return torch.mm(pred, self.w.lm_head.t()).view(b, t, -1)
 
     @torch.no_grad()
-    def prefill(self, idx_BxT: Tensor, max_new_tokens: int):
+    def prefill(self, idx_BxT: Tensor, max_new_tokens: int, state: Optional[DecodeState] = None):
         """Batched prompt prefill (reverse_sps/inference.py:615-701): returns the decode state and
-        the logits [B, V] that predict the first new token."""
+        the logits [B, V] that predict the first new token.  ``state``: caches of an earlier call
+        to fill again, used when their batch size and capacity fit."""
         d = self.dims
         idx = idx_BxT.to(self.device)
         b, t = idx.shape
@@ -322,7 +323,11 @@ class SPSGenerator:
         if total > d.block_size:
             raise ValueError(f"Cannot generate {max_new_tokens} new tokens from a prompt with "
                              f"{total - int(max_new_tokens)} real tokens when block size is {d.block_size}")
-        state = self.build_decode_state(b, total)
+        if state is not None and state.processed_tokens.shape[0] == b and state.max_tokens == total:
+            for t_ in (state.nw_len, state.nw_pos, state.br_len):
+                t_.zero_()
+        else:
+            state = self.build_decode_state(b, total)
         docs = left_padded_document_idx(idx, d.eos_token_id, d.pad_token_id)
         docs2 = docs.repeat_interleave(2, dim=1).contiguous()
         doc_mask = (real & (docs == docs[:, -1:])).to(torch.uint8).contiguous()
@@ -416,7 +421,6 @@ class SPSGenerator:
         s.ws = torch.zeros(ws_bytes, device=dev, dtype=torch.uint8)
         s.ws_bytes = ws_bytes
         self._step = s
-        self._graph = None
 
     def _step_body(self) -> None:
         """One token for every row: reads ``token`` / ``active`` of the bound buffers, leaves the
@@ -474,19 +478,16 @@ class SPSGenerator:
         return torch.where(s.active.unsqueeze(1), s.logits, torch.zeros_like(s.logits))
 
     # ------------------------------------------------------------------ generation
-    def _greedy(self, logits: Tensor, suppressed: Tensor) -> Tensor:
-        z = logits.float()
-        z.index_fill_(1, suppressed, float("-inf"))
-        return z.argmax(dim=-1)
-
     @torch.no_grad()
     def generate(self, idx_BxT: Tensor, max_new_tokens: int, *, stop_on_eos: bool = True,
                  forbidden_token_ids: Optional[Tensor] = None, do_sample: bool = False,
                  use_graph: bool = True, timings: Optional[dict] = None) -> Tensor:
         """Greedy generation: [B, T + max_new_tokens], pad after a row has emitted EOS when
-        ``stop_on_eos`` (utils/generation.py:121-197).  ``timings`` (optional dict) receives
-        CUDA-event times in ms: ``prefill``, ``decode`` (everything after it) and ``decode_steps``
-        (the ``n_steps`` per-token steps alone)."""
+        ``stop_on_eos`` (utils/generation.py:121-197).  The caches, the step buffers and the
+        captured graph are kept for the next call with the same batch size, cache capacity and
+        sampling options, which then pays neither allocation nor capture.  ``timings`` (optional
+        dict) receives CUDA-event times in ms: ``prefill``, ``decode`` (everything after it) and
+        ``decode_steps`` (the ``n_steps`` per-token steps alone)."""
         if do_sample:
             raise NotImplementedError("only greedy decoding is implemented")
         if max_new_tokens < 0:
@@ -496,71 +497,91 @@ class SPSGenerator:
         if max_new_tokens == 0:
             return idx.clone()
         b = idx.shape[0]
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
-        ev[0].record()
-        state, next_logits = self.prefill(idx, max_new_tokens)
-        ev[1].record()
-        self._bind_step(state)
-        s = self._step
-        sup = [d.predict_token_id, d.pad_token_id]
+        sup = [d.predict_token_id, d.pad_token_id]                          # inference.py:893-902
         if forbidden_token_ids is not None:
             sup += [int(x) for x in forbidden_token_ids.reshape(-1).tolist()]
-        suppressed = torch.tensor(sorted(set(sup)), device=self.device, dtype=torch.long)
-        generated = torch.full((b, max_new_tokens), d.pad_token_id, device=self.device, dtype=idx.dtype)
-        finished = torch.zeros(b, device=self.device, dtype=torch.bool)
-        step_idx = torch.zeros((1, 1), device=self.device, dtype=torch.long)
-        pad_tok = torch.full((b,), d.pad_token_id, device=self.device, dtype=torch.long)
-        next_logits = next_logits.clone()
-
-        def sample():
-            live = ~finished
-            tok = torch.where(live, self._greedy(next_logits, suppressed), pad_tok)
-            generated.scatter_(1, step_idx.expand(b, 1), tok.view(b, 1).to(generated.dtype))
-            newly = live & (tok == d.eos_token_id) if stop_on_eos else torch.zeros_like(live)
-            return tok, live & ~newly, newly
-
-        def body():
-            tok, decode_active, newly = sample()
-            s.token.copy_(tok)
-            s.active.copy_(decode_active)
-            self._step_body()
-            torch.where(decode_active.unsqueeze(1), s.logits, next_logits, out=next_logits)
-            finished.logical_or_(newly)
-            step_idx.add_(1)
-
+        sup = tuple(sorted(set(sup)))
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        ev[0].record()
+        g = self._session
+        reuse = g is not None and g.state.processed_tokens.shape[0] == b
+        state, next_logits = self.prefill(idx, max_new_tokens, state=g.state if reuse else None)
+        ev[1].record()
+        key = (b, state.max_tokens, int(max_new_tokens), bool(stop_on_eos), sup, bool(use_graph))
+        if g is None or g.state is not state or g.key != key:
+            g = self._new_session(state, key)
+        s = self._step
+        g.next_logits.copy_(next_logits)
+        g.generated.fill_(d.pad_token_id)
+        g.finished.fill_(False)
+        g.step_idx.zero_()
         n_steps = max_new_tokens - 1          # the last token is sampled without a further decode
-        if n_steps > 0 and use_graph:
+        if n_steps > 0 and use_graph and g.graph is None:
             # warm-up with every row marked finished: the chain runs, nothing is sampled or stored
-            finished.fill_(True)
+            g.finished.fill_(True)
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(side):
                 for _ in range(2):
-                    body()
+                    self._token_body(g)
             torch.cuda.current_stream(self.device).wait_stream(side)
-            finished.fill_(False)
-            step_idx.zero_()
-            generated.fill_(d.pad_token_id)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                body()
-            # capture does not execute: replay once per token
-            ev[2].record()
-            for _ in range(n_steps):
-                graph.replay()
-            ev[3].record()
-            self._graph = graph
-        else:
-            ev[2].record()
-            for _ in range(n_steps):
-                body()
-            ev[3].record()
-        sample()
+            g.finished.fill_(False)
+            g.step_idx.zero_()
+            g.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g.graph):          # capture records, it does not execute
+                self._token_body(g)
+        ev[2].record()
+        for _ in range(n_steps):
+            if use_graph:
+                g.graph.replay()
+            else:
+                self._token_body(g)
+        ev[3].record()
+        self._sample(g)
         ev[4].record()
         if timings is not None:
             torch.cuda.synchronize(self.device)
             timings["prefill"] = ev[0].elapsed_time(ev[1])
-            timings["decode"] = ev[1].elapsed_time(ev[4])        # includes binding, warm-up and capture
+            timings["decode"] = ev[1].elapsed_time(ev[4])        # includes binding and capture, if any
             timings["decode_steps"] = ev[2].elapsed_time(ev[3])  # the n_steps token steps alone
             timings["n_steps"] = n_steps
-        return torch.cat([idx, generated], dim=1)
+        return torch.cat([idx, g.generated.to(idx.dtype)], dim=1)
+
+    def _new_session(self, state: DecodeState, key):
+        d, dev = self.dims, self.device
+        b, max_new = key[0], key[2]
+        if self._step is None or self._step.state is not state:
+            self._bind_step(state)
+        g = type("GenerationSession", (), {})()
+        g.state, g.key, g.graph = state, key, None
+        g.stop_on_eos = key[3]
+        g.suppressed = torch.tensor(list(key[4]), device=dev, dtype=torch.long)
+        g.generated = torch.full((b, max_new), d.pad_token_id, device=dev, dtype=torch.long)
+        g.finished = torch.zeros(b, device=dev, dtype=torch.bool)
+        g.step_idx = torch.zeros((1, 1), device=dev, dtype=torch.long)
+        g.pad_tok = torch.full((b,), d.pad_token_id, device=dev, dtype=torch.long)
+        g.next_logits = torch.zeros((b, d.vocab_size), device=dev, dtype=self.param_dtype)
+        self._session = g
+        return g
+
+    def _sample(self, g):
+        """utils/generation.py:171-181 with greedy sampling (utils/sampling.py:55-83)."""
+        live = ~g.finished
+        z = g.next_logits.float()
+        z.index_fill_(1, g.suppressed, float("-inf"))
+        tok = torch.where(live, z.argmax(dim=-1), g.pad_tok)
+        g.generated.scatter_(1, g.step_idx.expand(tok.shape[0], 1), tok.view(-1, 1))
+        newly = live & (tok == self.dims.eos_token_id) if g.stop_on_eos else torch.zeros_like(live)
+        return tok, live & ~newly, newly
+
+    def _token_body(self, g) -> None:
+        """Sample one token per row, run the decode step on it, keep its logits for the next
+        (utils/generation.py:171-195); reads and writes only buffers of the session."""
+        s = self._step
+        tok, decode_active, newly = self._sample(g)
+        s.token.copy_(tok)
+        s.active.copy_(decode_active)
+        self._step_body()
+        torch.where(decode_active.unsqueeze(1), s.logits, g.next_logits, out=g.next_logits)
+        g.finished.logical_or_(newly)
+        g.step_idx.add_(1)

@@ -24,6 +24,40 @@ PREFILL_CONFIGS = {
 DECODE_CONFIGS = {
     "cfg2_segmented_decode": (128, 16, 64, 64, 512, 4096),
 }
+# name -> model dims, batch, prompt length, new tokens.  The shapes of the reference's generation
+# benchmark (prompt 1024, greedy, bf16 cache, w = 64; scripts/benchmark/benchmark_generation_speed.py)
+# on the decoder the reference implements (RMSNorm, rotary, SwiGLU, tied head).
+GENERATION_CONFIGS = {
+    "cfg3_xl_generation": dict(block_size=1280, vocab_size=50304, n_layer=24, n_head=16, hidden_size=2048,
+                               intermediate_size=8192, eos_token_id=50256, pad_token_id=50303,
+                               predict_token_id=50257, window_size=64, batch=32, prompt=1024, new_tokens=256),
+    "generation_small": dict(block_size=160, vocab_size=2048, n_layer=2, n_head=4, hidden_size=512,
+                             intermediate_size=1024, eos_token_id=2000, pad_token_id=2047,
+                             predict_token_id=2001, window_size=16, batch=4, prompt=96, new_tokens=24),
+}
+
+
+def generation_forbidden_ids(cfg: dict) -> list:
+    """Token ids the reference's speed benchmark never lets the model emit: everything above EOS,
+    the pad and the <predict> id (benchmark_generation_speed.py:204-220)."""
+    ids = set(range(cfg["eos_token_id"] + 1, cfg["vocab_size"]))
+    ids.update((cfg["pad_token_id"], cfg["predict_token_id"]))
+    return sorted(ids)
+
+
+def generation_prompts(cfg: dict, batch: int, seed: int) -> np.ndarray:
+    """[batch, prompt] int64 ids uniform in [0, eos): single-document prompts without special ids."""
+    rng = np.random.default_rng(seed)
+    return rng.integers(0, cfg["eos_token_id"], size=(batch, cfg["prompt"]), dtype=np.int64)
+
+
+def generation_step_bytes(cfg: dict, batch: int, live_tokens: float) -> float:
+    """Bytes one decode step must read at least: every parameter once (bf16; the embedding table is
+    read once as the head) plus the live K/V rows of every layer (retained cache + ring)."""
+    c, i, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["n_layer"]
+    params = L * (4 * c * c + 3 * c * i) + cfg["vocab_size"] * c
+    kv = L * batch * (live_tokens + cfg["window_size"]) * c * 2
+    return 2.0 * (params + kv)
 
 
 def geometric_docs(batch: int, tokens: int, mean: Optional[float], seed: int) -> np.ndarray:
