@@ -192,19 +192,25 @@ int spsattn_decode_fwd_noalloc(const void* q, int nq, float* out,
                                int* device_status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
- * One layer of an SPS-family decode step: the segmented attention of spsattn_decode_fwd with the
- * cache update of spsattn_kv_update folded into its merge pass, and the output written in the
- * type the output projection consumes.  Stands in for the pair of calls the reference makes per
- * layer and token (reverse_sps/inference.py:434-477: _attend_pair_from_decode_state, then
+ * One layer of an SPS-family decode step in a single launch: the segmented attention of
+ * spsattn_decode_fwd, merged by the last block of each (sequence, head) instead of a second
+ * kernel, with the cache update of spsattn_kv_update folded into that merge, and the output written
+ * in the type the output projection consumes.  Stands in for the pair of calls the reference makes
+ * per layer and token (reverse_sps/inference.py:434-477: _attend_pair_from_decode_state, then
  * _update_normal_memory + _update_predict_memory -> fused_sps_kv_update).
  *
  * `append` (NULL = attention only) names the ring and the retained cache of this layer, which
  * must be the buffers the segments read, and this step's K/V rows for them.  The attention sees
  * the caches as they are before the update; afterwards, for every active sequence, the rows are
- * stored and the counters advanced exactly as spsattn_kv_update does.  All cache reads happen in
- * the first launch and the counters are snapshotted there, the stores happen in the second.
- * out_dtype: SPSATTN_DTYPE_FP32, or the queries' 16-bit type.  Workspace:
- * spsattn_decode_step_workspace_bytes.  16-bit caches only.
+ * stored and the counters advanced exactly as spsattn_kv_update does.  A (sequence, head) is
+ * updated only after all of its blocks have read the counters and finished reading its rows; the
+ * per-sequence ring counters only after all heads of the sequence have.  No block waits for another.
+ * out_dtype: SPSATTN_DTYPE_FP32, or the queries' 16-bit type.  16-bit caches only.
+ *
+ * Workspace: spsattn_decode_step_workspace_bytes; its last (S*H + S) * 4 bytes (rounded up to 256)
+ * are completion tickets that must be ZERO before the first call that uses the buffer — zero the
+ * whole workspace once after allocating it — and are left zero by every call that completes, so
+ * the same buffer serves every later call on the same stream without further clearing.
  * ------------------------------------------------------------------------------------------- */
 typedef struct spsattn_kv_append {
   void* nw_k;               /* device ring      [S, H, window_storage, D] */

@@ -10,10 +10,12 @@
 // (sequence, head) and writes the output (fp32, or 16-bit for a caller that feeds a projection).
 // Lengths are read on the device, so the grid is sized from the host-side caps and blocks past
 // the live length return at once.
-// Optionally the merge kernel also performs the decode step's cache update (ring insert, retained
-// append, counters) for its (sequence, head): every read of the caches happened in the split
-// kernel, which has finished, and the counters the merge needs were snapshotted there, so no
-// block of the merge kernel reads a counter another block writes.
+// The decode-step form is a single launch: every block of a (sequence, head) takes a ticket when
+// it is done and the last one merges the records itself, and (when asked) also performs the step's
+// cache update for its (sequence, head) — ring insert, retained append, counters.  By then every
+// block of that (sequence, head) has read the counters and finished reading the rows, which is
+// what makes the in-place update safe; the per-sequence ring counters are advanced by the last
+// (sequence, head) of the sequence to finish, through a second ticket.  Nothing waits on a ticket.
 // Reference computation: src/modeling/models/utils/decode_attention.py:191-368 and, for the
 // update, src/modeling/models/utils/decode_attention_fast.py:34-136.
 #pragma once
@@ -60,7 +62,7 @@ struct DecodeParams {
   void* out;           // [S, nq, H, D] fp32, or 16-bit in the queries' format when out16 is set
   int out16;
   float* partial;      // [S*H][n_chunks][nq][D + 2]
-  int4* snap;          // [S*H] (live rows, ring insert row, ring length, retained length) or null
+  int* tickets;        // [S*H + S] zero before the first launch, left zero; null = separate merge launch
   DecodeAppend app;
   DecodeSeg seg[kMaxSegments];
   const void* extra_k[kMaxExtras];
@@ -78,8 +80,55 @@ __device__ __forceinline__ int live_rows(const DecodeSeg& sg, int s, int h, int 
   return len < sg.max_rows ? (int)len : sg.max_rows;
 }
 
+// Merge the chunk records of one (sequence, head) and write its outputs; `nthreads` threads of
+// one block cooperate.  Records are read past L1 (other blocks may have written them), eight
+// chunks at a time with all their loads in flight together, so a merge costs about one round
+// trip to L2 instead of one per chunk.
 template <int D, int NQ, bool FP16>
-__global__ void __launch_bounds__(kDecodeThreads)
+__device__ __forceinline__ void merge_records(const DecodeParams& prm, int sh, int s, int h, int n_total,
+                                              int tid, int nthreads) {
+  constexpr int G = 8;
+  int n_chunks = (n_total + prm.chunk_rows - 1) / prm.chunk_rows;
+  if (n_chunks < 1) n_chunks = 1;
+  for (int idx = tid; idx < NQ * D; idx += nthreads) {
+    const int qi = idx / D, d = idx % D;
+    const float* rec0 = prm.partial + (size_t)sh * prm.n_chunks * NQ * (D + 2) + qi * (D + 2);
+    float m_run = -1.0e30f, l_run = 0.f, a_run = 0.f;
+    for (int c0 = 0; c0 < n_chunks; c0 += G) {
+      float m[G], l[G], a[G];
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        const int c = min(c0 + j, n_chunks - 1);      // clamped: the tail repeats a valid record
+        const float* rec = rec0 + (size_t)c * NQ * (D + 2);
+        m[j] = __ldcg(rec);
+        l[j] = __ldcg(rec + 1);
+        a[j] = __ldcg(rec + 2 + d);
+      }
+      float mx = m_run;
+#pragma unroll
+      for (int j = 0; j < G; ++j) mx = fmaxf(mx, m[j]);
+      const float keep = fast_exp2(m_run - mx);
+      l_run *= keep;
+      a_run *= keep;
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        const float f = c0 + j < n_chunks ? fast_exp2(m[j] - mx) : 0.f;
+        l_run = fmaf(l[j], f, l_run);
+        a_run = fmaf(a[j], f, a_run);
+      }
+      m_run = mx;
+    }
+    const float o = l_run > 0.f ? a_run / l_run : 0.f;
+    const size_t off = (((size_t)s * NQ + qi) * prm.H + h) * D + d;
+    if (prm.out16)
+      reinterpret_cast<uint16_t*>(prm.out)[off] = (uint16_t)(pack2<FP16>(o, 0.f) & 0xffffu);
+    else
+      reinterpret_cast<float*>(prm.out)[off] = o;
+  }
+}
+
+template <int D, int NQ, bool FP16>
+__global__ void __launch_bounds__(kDecodeThreads, 5)
 decode_split_kernel(const DecodeParams prm) {
   constexpr int LPR = D / 8;          // lanes per row
   constexpr int RPI = 32 / LPR;       // rows per warp load instruction
@@ -89,7 +138,8 @@ decode_split_kernel(const DecodeParams prm) {
 
   const int sh = blockIdx.x;
   const int s = sh / prm.H, h = sh % prm.H;
-  const int chunk = blockIdx.y;
+  // highest chunk first: blocks past the live length retire at once, at the start of the launch
+  const int chunk = (int)gridDim.y - 1 - (int)blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane / LPR;           // row inside a load instruction
   const int dl = (lane % LPR) * 8;    // first of this lane's 8 dims
@@ -100,248 +150,250 @@ decode_split_kernel(const DecodeParams prm) {
   for (int x = 0; x < kMaxSegments; ++x)
     seg_start[x + 1] = seg_start[x] + (x < prm.n_segments ? live_rows(prm.seg[x], s, h, prm.H) : 0);
   const int n_total = seg_start[kMaxSegments];
-  if (prm.snap != nullptr && chunk == 0 && tid == 0) {
-    // the counters as they are before this step's update; the merge kernel reads only these
-    long long ring_len = 0, ring_pos = 0, ret_len = 0;
-    if (prm.app.br_len != nullptr) ret_len = prm.app.br_len[(size_t)s * prm.H + h];
+  const int c_lo = chunk * prm.chunk_rows;
+  const bool dead = chunk > 0 && c_lo >= n_total;
+  if (dead && prm.tickets == nullptr) return;
+  const int c_hi = min(c_lo + prm.chunk_rows, n_total);
+  // the counters as they are before this step's update (any block may be the one that applies it)
+  long long ring_len = 0, ring_pos = 0, ret_len = 0;
+  if (prm.app.br_len != nullptr) {
+    ret_len = prm.app.br_len[(size_t)s * prm.H + h];
     if (prm.app.window_tokens > 0) {
       ring_len = prm.app.nw_len[s];
       ring_pos = prm.app.nw_pos[s];
     }
-    const long long ins = ring_len >= prm.app.window_tokens ? ring_pos : ring_len;
-    const long long big = 0x7fffffffLL;
-    prm.snap[sh] = make_int4(n_total, (int)(ins < 0 ? -1 : (ins > big ? big : ins)),
-                             (int)(ring_len > big ? big : ring_len),
-                             (int)(ret_len < 0 ? -1 : (ret_len > big ? big : ret_len)));
-  }
-  const int c_lo = chunk * prm.chunk_rows;
-  if (chunk > 0 && c_lo >= n_total) return;
-  const int c_hi = min(c_lo + prm.chunk_rows, n_total);
-
-  // queries, pre-scaled so scores are in the log2 domain
-  float q[NQ][8];
-#pragma unroll
-  for (int qi = 0; qi < NQ; ++qi) {
-    const uint4 u = *reinterpret_cast<const uint4*>(
-        reinterpret_cast<const uint16_t*>(prm.q) + (((size_t)s * NQ + qi) * prm.H + h) * D + dl);
-    unpack2<FP16>(u.x, q[qi][0], q[qi][1]);
-    unpack2<FP16>(u.y, q[qi][2], q[qi][3]);
-    unpack2<FP16>(u.z, q[qi][4], q[qi][5]);
-    unpack2<FP16>(u.w, q[qi][6], q[qi][7]);
-#pragma unroll
-    for (int x = 0; x < 8; ++x) q[qi][x] *= prm.scale_log2;
   }
 
-  float m_run[NQ], l_run[NQ], acc[NQ][8];
-#pragma unroll
-  for (int qi = 0; qi < NQ; ++qi) {
-    m_run[qi] = -1.0e30f;
-    l_run[qi] = 0.f;
-#pragma unroll
-    for (int x = 0; x < 8; ++x) acc[qi][x] = 0.f;
-  }
-
-  // one batch of U rows (one per unroll slot) for this lane group
-  auto process = [&](const uint16_t* kb, const uint16_t* vb, int64_t row_stride, int r0, int r_hi,
-                     uint32_t qmask) {
-    uint4 kr[U], vr[U];
-    bool valid[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int r = r0 + u * (4 * RPI);
-      valid[u] = r < r_hi;
-      if (valid[u]) {
-        kr[u] = __ldg(reinterpret_cast<const uint4*>(kb + (size_t)r * row_stride + dl));
-        vr[u] = __ldg(reinterpret_cast<const uint4*>(vb + (size_t)r * row_stride + dl));
-      } else {
-        kr[u] = make_uint4(0, 0, 0, 0);
-        vr[u] = make_uint4(0, 0, 0, 0);
-      }
-    }
-    float sc[NQ][U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      float kf[8];
-      unpack2<FP16>(kr[u].x, kf[0], kf[1]);
-      unpack2<FP16>(kr[u].y, kf[2], kf[3]);
-      unpack2<FP16>(kr[u].z, kf[4], kf[5]);
-      unpack2<FP16>(kr[u].w, kf[6], kf[7]);
-#pragma unroll
-      for (int qi = 0; qi < NQ; ++qi) {
-        float d = 0.f;
-#pragma unroll
-        for (int x = 0; x < 8; ++x) d = fmaf(q[qi][x], kf[x], d);
-#pragma unroll
-        for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-        sc[qi][u] = (valid[u] && ((qmask >> qi) & 1u)) ? d : -INFINITY;
-      }
-    }
-    float pr[NQ][U], alpha[NQ];
+  if (!dead) {   // blocks past the live length only take their ticket below
+    // queries, pre-scaled so scores are in the log2 domain
+    float q[NQ][8];
 #pragma unroll
     for (int qi = 0; qi < NQ; ++qi) {
-      float mx = m_run[qi];
+      const uint4 u = *reinterpret_cast<const uint4*>(
+          reinterpret_cast<const uint16_t*>(prm.q) + (((size_t)s * NQ + qi) * prm.H + h) * D + dl);
+      unpack2<FP16>(u.x, q[qi][0], q[qi][1]);
+      unpack2<FP16>(u.y, q[qi][2], q[qi][3]);
+      unpack2<FP16>(u.z, q[qi][4], q[qi][5]);
+      unpack2<FP16>(u.w, q[qi][6], q[qi][7]);
 #pragma unroll
-      for (int u = 0; u < U; ++u) mx = fmaxf(mx, sc[qi][u]);
-      alpha[qi] = fast_exp2(m_run[qi] - mx);
-      float sum = 0.f;
+      for (int x = 0; x < 8; ++x) q[qi][x] *= prm.scale_log2;
+    }
+
+    float m_run[NQ], l_run[NQ], acc[NQ][8];
+#pragma unroll
+    for (int qi = 0; qi < NQ; ++qi) {
+      m_run[qi] = -1.0e30f;
+      l_run[qi] = 0.f;
+#pragma unroll
+      for (int x = 0; x < 8; ++x) acc[qi][x] = 0.f;
+    }
+
+    // one batch of U rows (one per unroll slot) for this lane group
+    auto process = [&](const uint16_t* kb, const uint16_t* vb, int64_t row_stride, int r0, int r_hi,
+                       uint32_t qmask) {
+      uint4 kr[U], vr[U];
+      bool valid[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        pr[qi][u] = fast_exp2(sc[qi][u] - mx);
-        sum += pr[qi][u];
+        const int r = r0 + u * (4 * RPI);
+        valid[u] = r < r_hi;
+        if (valid[u]) {
+          kr[u] = __ldg(reinterpret_cast<const uint4*>(kb + (size_t)r * row_stride + dl));
+          vr[u] = __ldg(reinterpret_cast<const uint4*>(vb + (size_t)r * row_stride + dl));
+        } else {
+          kr[u] = make_uint4(0, 0, 0, 0);
+          vr[u] = make_uint4(0, 0, 0, 0);
+        }
       }
-      l_run[qi] = l_run[qi] * alpha[qi] + sum;
-      m_run[qi] = mx;
+      float sc[NQ][U];
 #pragma unroll
-      for (int x = 0; x < 8; ++x) acc[qi][x] *= alpha[qi];
-    }
+      for (int u = 0; u < U; ++u) {
+        float kf[8];
+        unpack2<FP16>(kr[u].x, kf[0], kf[1]);
+        unpack2<FP16>(kr[u].y, kf[2], kf[3]);
+        unpack2<FP16>(kr[u].z, kf[4], kf[5]);
+        unpack2<FP16>(kr[u].w, kf[6], kf[7]);
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      float vf[8];
-      unpack2<FP16>(vr[u].x, vf[0], vf[1]);
-      unpack2<FP16>(vr[u].y, vf[2], vf[3]);
-      unpack2<FP16>(vr[u].z, vf[4], vf[5]);
-      unpack2<FP16>(vr[u].w, vf[6], vf[7]);
+        for (int qi = 0; qi < NQ; ++qi) {
+          float d = 0.f;
 #pragma unroll
-      for (int qi = 0; qi < NQ; ++qi)
+          for (int x = 0; x < 8; ++x) d = fmaf(q[qi][x], kf[x], d);
 #pragma unroll
-        for (int x = 0; x < 8; ++x) acc[qi][x] = fmaf(pr[qi][u], vf[x], acc[qi][x]);
-    }
-  };
+          for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          sc[qi][u] = (valid[u] && ((qmask >> qi) & 1u)) ? d : -INFINITY;
+        }
+      }
+      float pr[NQ][U], alpha[NQ];
+#pragma unroll
+      for (int qi = 0; qi < NQ; ++qi) {
+        float mx = m_run[qi];
+#pragma unroll
+        for (int u = 0; u < U; ++u) mx = fmaxf(mx, sc[qi][u]);
+        alpha[qi] = fast_exp2(m_run[qi] - mx);
+        float sum = 0.f;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          pr[qi][u] = fast_exp2(sc[qi][u] - mx);
+          sum += pr[qi][u];
+        }
+        l_run[qi] = l_run[qi] * alpha[qi] + sum;
+        m_run[qi] = mx;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) acc[qi][x] *= alpha[qi];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float vf[8];
+        unpack2<FP16>(vr[u].x, vf[0], vf[1]);
+        unpack2<FP16>(vr[u].y, vf[2], vf[3]);
+        unpack2<FP16>(vr[u].z, vf[4], vf[5]);
+        unpack2<FP16>(vr[u].w, vf[6], vf[7]);
+#pragma unroll
+        for (int qi = 0; qi < NQ; ++qi)
+#pragma unroll
+          for (int x = 0; x < 8; ++x) acc[qi][x] = fmaf(pr[qi][u], vf[x], acc[qi][x]);
+      }
+    };
 
 #pragma unroll
-  for (int x = 0; x < kMaxSegments; ++x) {
-    if (x >= prm.n_segments) break;
-    const int lo = max(c_lo, seg_start[x]) - seg_start[x];
-    const int hi = min(c_hi, seg_start[x + 1]) - seg_start[x];
-    if (lo >= hi) continue;
-    const DecodeSeg& sg = prm.seg[x];
-    const int64_t base = (sg.seq_offset ? sg.seq_offset[s] : (int64_t)s * sg.seq_stride) +
-                         (int64_t)h * sg.head_stride;
-    const uint16_t* kb = reinterpret_cast<const uint16_t*>(sg.k) + base;
-    const uint16_t* vb = reinterpret_cast<const uint16_t*>(sg.v) + base;
-    for (int r = lo + warp * RPI + g; r - (warp * RPI + g) < hi; r += STEP)
-      process(kb, vb, sg.row_stride, r, hi, sg.query_mask);
-  }
-  if (chunk == 0 && warp == 0) {
-    // the current-token entries: one row each, handled by lane group 0 of warp 0
-    for (int e = 0; e < prm.n_extras; ++e) {
-      const uint16_t* kb = reinterpret_cast<const uint16_t*>(prm.extra_k[e]) + (size_t)sh * D;
-      const uint16_t* vb = reinterpret_cast<const uint16_t*>(prm.extra_v[e]) + (size_t)sh * D;
-      process(kb, vb, 0, g, 1, prm.extra_mask[e]);
+    for (int x = 0; x < kMaxSegments; ++x) {
+      if (x >= prm.n_segments) break;
+      const int lo = max(c_lo, seg_start[x]) - seg_start[x];
+      const int hi = min(c_hi, seg_start[x + 1]) - seg_start[x];
+      if (lo >= hi) continue;
+      const DecodeSeg& sg = prm.seg[x];
+      const int64_t base = (sg.seq_offset ? sg.seq_offset[s] : (int64_t)s * sg.seq_stride) +
+                           (int64_t)h * sg.head_stride;
+      const uint16_t* kb = reinterpret_cast<const uint16_t*>(sg.k) + base;
+      const uint16_t* vb = reinterpret_cast<const uint16_t*>(sg.v) + base;
+      for (int r = lo + warp * RPI + g; r - (warp * RPI + g) < hi; r += STEP)
+        process(kb, vb, sg.row_stride, r, hi, sg.query_mask);
     }
-  }
-
-  // merge the lane groups of a warp, then the four warps, then write the record
-#pragma unroll
-  for (int qi = 0; qi < NQ; ++qi) {
-#pragma unroll
-    for (int o = LPR; o < 32; o <<= 1) {
-      const float m_o = __shfl_xor_sync(0xffffffffu, m_run[qi], o);
-      const float l_o = __shfl_xor_sync(0xffffffffu, l_run[qi], o);
-      const float mx = fmaxf(m_run[qi], m_o);
-      const float a = fast_exp2(m_run[qi] - mx), bsc = fast_exp2(m_o - mx);
-      l_run[qi] = l_run[qi] * a + l_o * bsc;
-#pragma unroll
-      for (int x = 0; x < 8; ++x) {
-        const float acc_o = __shfl_xor_sync(0xffffffffu, acc[qi][x], o);
-        acc[qi][x] = acc[qi][x] * a + acc_o * bsc;
+    if (chunk == 0 && warp == 0) {
+      // the current-token entries: one row each, handled by lane group 0 of warp 0
+      for (int e = 0; e < prm.n_extras; ++e) {
+        const uint16_t* kb = reinterpret_cast<const uint16_t*>(prm.extra_k[e]) + (size_t)sh * D;
+        const uint16_t* vb = reinterpret_cast<const uint16_t*>(prm.extra_v[e]) + (size_t)sh * D;
+        process(kb, vb, 0, g, 1, prm.extra_mask[e]);
       }
-      m_run[qi] = mx;
     }
-  }
-  __shared__ float s_m[4][NQ], s_l[4][NQ], s_acc[4][NQ][D];
-  if (g == 0) {
+
+    // merge the lane groups of a warp, then the four warps, then write the record
 #pragma unroll
     for (int qi = 0; qi < NQ; ++qi) {
-      if (lane == 0) {
-        s_m[warp][qi] = m_run[qi];
-        s_l[warp][qi] = l_run[qi];
-      }
 #pragma unroll
-      for (int x = 0; x < 8; ++x) s_acc[warp][qi][dl + x] = acc[qi][x];
+      for (int o = LPR; o < 32; o <<= 1) {
+        const float m_o = __shfl_xor_sync(0xffffffffu, m_run[qi], o);
+        const float l_o = __shfl_xor_sync(0xffffffffu, l_run[qi], o);
+        const float mx = fmaxf(m_run[qi], m_o);
+        const float a = fast_exp2(m_run[qi] - mx), bsc = fast_exp2(m_o - mx);
+        l_run[qi] = l_run[qi] * a + l_o * bsc;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          const float acc_o = __shfl_xor_sync(0xffffffffu, acc[qi][x], o);
+          acc[qi][x] = acc[qi][x] * a + acc_o * bsc;
+        }
+        m_run[qi] = mx;
+      }
+    }
+    __shared__ float s_m[4][NQ], s_l[4][NQ], s_acc[4][NQ][D];
+    if (g == 0) {
+#pragma unroll
+      for (int qi = 0; qi < NQ; ++qi) {
+        if (lane == 0) {
+          s_m[warp][qi] = m_run[qi];
+          s_l[warp][qi] = l_run[qi];
+        }
+#pragma unroll
+        for (int x = 0; x < 8; ++x) s_acc[warp][qi][dl + x] = acc[qi][x];
+      }
+    }
+    __syncthreads();
+    float* rec = prm.partial + ((size_t)sh * prm.n_chunks + chunk) * NQ * (D + 2);
+    for (int idx = tid; idx < NQ * D; idx += kDecodeThreads) {
+      const int qi = idx / D, d = idx % D;
+      float mx = s_m[0][qi];
+#pragma unroll
+      for (int w = 1; w < 4; ++w) mx = fmaxf(mx, s_m[w][qi]);
+      float a = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = fast_exp2(s_m[w][qi] - mx);
+        a += s_acc[w][qi][d] * f;
+        l += s_l[w][qi] * f;
+      }
+      rec[qi * (D + 2) + 2 + d] = a;
+      if (d == 0) {
+        rec[qi * (D + 2)] = mx;
+        rec[qi * (D + 2) + 1] = l;
+      }
     }
   }
+
+  if (prm.tickets == nullptr) return;     // a separate launch merges
+  // Last block of this (sequence, head) to finish merges.  Every block takes a ticket, also
+  // those past the live length, so that all of them have read the counters before any update.
+  // (the barrier orders the block's record stores before thread 0's fence, which is cumulative)
+  if (!dead) __syncthreads();
+  __shared__ int s_last;
+  if (tid == 0) {
+    if (!dead) __threadfence();
+    const bool last = atomicAdd(&prm.tickets[sh], 1) == (int)gridDim.y - 1;
+    if (last) __threadfence();
+    s_last = last;
+  }
   __syncthreads();
-  float* rec = prm.partial + ((size_t)sh * prm.n_chunks + chunk) * NQ * (D + 2);
-  for (int idx = tid; idx < NQ * D; idx += kDecodeThreads) {
-    const int qi = idx / D, d = idx % D;
-    float mx = s_m[0][qi];
-#pragma unroll
-    for (int w = 1; w < 4; ++w) mx = fmaxf(mx, s_m[w][qi]);
-    float a = 0.f, l = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float f = fast_exp2(s_m[w][qi] - mx);
-      a += s_acc[w][qi][d] * f;
-      l += s_l[w][qi] * f;
+  if (!s_last) return;
+  merge_records<D, NQ, FP16>(prm, sh, s, h, n_total, tid, kDecodeThreads);
+  const DecodeAppend& ap = prm.app;
+  const bool append = ap.br_k != nullptr && ap.active[s] != 0;
+  const bool full = ring_len >= ap.window_tokens;
+  if (append) {
+    const long long ins = full ? ring_pos : ring_len;
+    for (int d = tid; d < D; d += kDecodeThreads) {
+      const size_t src = (size_t)sh * D + d;
+      if (ap.window_tokens > 0 && ins >= 0 && ins < ap.window_storage) {
+        const size_t dst = ((size_t)sh * ap.window_storage + (size_t)ins) * D + d;
+        ap.nw_k[dst] = ap.k_window[src];
+        ap.nw_v[dst] = ap.v_window[src];
+      }
+      if (ret_len >= 0 && ret_len < ap.retained_storage) {
+        const size_t dst = ((size_t)sh * ap.retained_storage + (size_t)ret_len) * D + d;
+        ap.br_k[dst] = ap.k_retained[src];
+        ap.br_v[dst] = ap.v_retained[src];
+      }
     }
-    rec[qi * (D + 2) + 2 + d] = a;
-    if (d == 0) {
-      rec[qi * (D + 2)] = mx;
-      rec[qi * (D + 2) + 1] = l;
+  }
+  if (tid == 0) {
+    prm.tickets[sh] = 0;                  // ready for the next launch
+    if (append && ret_len < ap.retained_storage) ap.br_len[sh] = ret_len + 1;
+    if (ap.br_k != nullptr && ap.window_tokens > 0) {
+      // the ring counters belong to the sequence: the last of its heads to get here advances them
+      __threadfence();
+      int* seq_ticket = prm.tickets + (size_t)prm.S * prm.H + s;
+      if (atomicAdd(seq_ticket, 1) == prm.H - 1) {
+        *seq_ticket = 0;
+        if (append) {
+          if (full)
+            ap.nw_pos[s] = (ring_pos + 1) % ap.window_tokens;
+          else
+            ap.nw_len[s] = ring_len + 1;
+        }
+      }
     }
   }
 }
 
-// One block of D threads per (sequence, head): merge the chunk records of each query, then
-// (when asked) store this step's K/V rows into the caches and advance the counters.
+// Separate merge launch for callers whose workspace carries no tickets: one block of D threads
+// per (sequence, head).
 template <int D, int NQ, bool FP16>
 __global__ void __launch_bounds__(D)
 decode_merge_kernel(const DecodeParams prm) {
   const int sh = blockIdx.x;
   const int s = sh / prm.H, h = sh % prm.H;
-  const int d = threadIdx.x;
-  int4 snap = make_int4(0, 0, 0, 0);
   int n_total = 0;
-  if (prm.snap != nullptr) {
-    snap = prm.snap[sh];
-    n_total = snap.x;
-  } else {
-    for (int x = 0; x < prm.n_segments; ++x) n_total += live_rows(prm.seg[x], s, h, prm.H);
-  }
-  int n_chunks = (n_total + prm.chunk_rows - 1) / prm.chunk_rows;
-  if (n_chunks < 1) n_chunks = 1;
-#pragma unroll
-  for (int qi = 0; qi < NQ; ++qi) {
-    const float* rec0 = prm.partial + (size_t)sh * prm.n_chunks * NQ * (D + 2) + qi * (D + 2);
-    float mx = -1.0e30f;
-    for (int c = 0; c < n_chunks; ++c) mx = fmaxf(mx, rec0[(size_t)c * NQ * (D + 2)]);
-    float a = 0.f, l = 0.f;
-    for (int c = 0; c < n_chunks; ++c) {
-      const float* rec = rec0 + (size_t)c * NQ * (D + 2);
-      const float f = fast_exp2(rec[0] - mx);
-      l += rec[1] * f;
-      a += rec[2 + d] * f;
-    }
-    const float o = l > 0.f ? a / l : 0.f;
-    const size_t off = (((size_t)s * NQ + qi) * prm.H + h) * D + d;
-    if (prm.out16)
-      reinterpret_cast<uint16_t*>(prm.out)[off] = (uint16_t)(pack2<FP16>(o, 0.f) & 0xffffu);
-    else
-      reinterpret_cast<float*>(prm.out)[off] = o;
-  }
-  const DecodeAppend& ap = prm.app;
-  if (ap.br_k == nullptr || ap.active[s] == 0) return;
-  const size_t src = (size_t)sh * D + d;
-  if (ap.window_tokens > 0 && snap.y >= 0 && snap.y < ap.window_storage) {
-    const size_t dst = ((size_t)sh * ap.window_storage + (size_t)snap.y) * D + d;
-    ap.nw_k[dst] = ap.k_window[src];
-    ap.nw_v[dst] = ap.v_window[src];
-  }
-  if (snap.w >= 0 && snap.w < ap.retained_storage) {
-    const size_t dst = ((size_t)sh * ap.retained_storage + (size_t)snap.w) * D + d;
-    ap.br_k[dst] = ap.k_retained[src];
-    ap.br_v[dst] = ap.v_retained[src];
-  }
-  if (d == 0) {
-    if (snap.w < ap.retained_storage) ap.br_len[sh] = (long long)snap.w + 1;
-    if (h == 0 && ap.window_tokens > 0) {
-      if (snap.z >= ap.window_tokens)
-        ap.nw_pos[s] = ((long long)snap.y + 1) % ap.window_tokens;
-      else
-        ap.nw_len[s] = (long long)snap.z + 1;
-    }
-  }
+  for (int x = 0; x < prm.n_segments; ++x) n_total += live_rows(prm.seg[x], s, h, prm.H);
+  merge_records<D, NQ, FP16>(prm, sh, s, h, n_total, threadIdx.x, D);
 }
 
 }  // namespace spsattn

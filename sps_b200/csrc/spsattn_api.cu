@@ -164,7 +164,7 @@ static int launch_decode(const DecodeParams& prm, cudaStream_t st) {
   dim3 grid((unsigned)(prm.S * prm.H), (unsigned)prm.n_chunks);
   decode_split_kernel<D, NQ, FP16><<<grid, kDecodeThreads, 0, st>>>(prm);
   cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
+  if (e != cudaSuccess || prm.tickets != nullptr) return (int)e;   // with tickets the last block merges
   decode_merge_kernel<D, NQ, FP16><<<(unsigned)(prm.S * prm.H), D, 0, st>>>(prm);
   return (int)cudaGetLastError();
 }
@@ -330,6 +330,10 @@ int spsattn_debug_visibility(uint8_t* vis, const void* doc_ids, int doc_is_i64, 
 
 // ------------------------------------------------------------------------------------------ decode
 
+static size_t decode_ticket_bytes(int S, int H) {
+  return align_up(((size_t)S * H + (size_t)S) * sizeof(int), 256);
+}
+
 static size_t decode_records_bytes(int S, int H, int D, int nq, const spsattn_segment* segs,
                                    int n_segments) {
   const long long rows = decode_max_rows(segs, n_segments);
@@ -348,14 +352,14 @@ size_t spsattn_decode_workspace_bytes(int S, int H, int D, int nq, const spsattn
 size_t spsattn_decode_step_workspace_bytes(int S, int H, int D, int nq, const spsattn_segment* segs,
                                            int n_segments) {
   if (S <= 0 || H <= 0 || D <= 0 || nq <= 0 || n_segments < 0 || (n_segments > 0 && !segs)) return 256;
-  return decode_records_bytes(S, H, D, nq, segs, n_segments) + align_up((size_t)S * H * sizeof(int4), 256);
+  return decode_records_bytes(S, H, D, nq, segs, n_segments) + decode_ticket_bytes(S, H);
 }
 
 // Shared body of the decode entry points.  out_dtype: 2 = fp32, else 16-bit in the queries' format.
 static int decode_impl(const void* q, int nq, void* out, int out_dtype, const spsattn_segment* segs,
                        int n_segments, const spsattn_extra* extras, int n_extras,
-                       const spsattn_kv_append* append, int S, int H, int D, int dtype, float sm_scale,
-                       void* workspace, size_t workspace_bytes, void* stream) {
+                       const spsattn_kv_append* append, bool single_launch, int S, int H, int D, int dtype,
+                       float sm_scale, void* workspace, size_t workspace_bytes, void* stream) {
   if (!q || !out) return SPSATTN_ERR_ARG;
   if (nq != 1 && nq != 2) return SPSATTN_ERR_ARG;
   if (S <= 0 || H <= 0) return SPSATTN_ERR_ARG;
@@ -404,8 +408,9 @@ static int decode_impl(const void* q, int nq, void* out, int out_dtype, const sp
   prm.n_chunks = (int)n_chunks;
   const size_t raw = (size_t)S * H * n_chunks * nq * (D + 2) * sizeof(float);
   const size_t records = align_up(raw, 256);
-  const size_t need = append ? records + (size_t)S * H * sizeof(int4) : raw;
+  const size_t need = single_launch ? records + decode_ticket_bytes(S, H) : raw;
   if (!workspace || workspace_bytes < need) return SPSATTN_ERR_WORKSPACE;
+  if (append && !single_launch) return SPSATTN_ERR_ARG;
   if (!aligned16(workspace)) return SPSATTN_ERR_ALIGN;
   if (append) {
     const spsattn_kv_append& a = *append;
@@ -433,8 +438,8 @@ static int decode_impl(const void* q, int nq, void* out, int out_dtype, const sp
     d.window_storage = a.window_storage;
     d.retained_storage = a.retained_storage;
     d.window_tokens = a.window_tokens > 0 ? a.window_tokens : 0;
-    prm.snap = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(workspace) + records);
   }
+  if (single_launch) prm.tickets = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + records);
   prm.q = q;
   prm.out = out;
   prm.out16 = out_dtype != SPSATTN_DTYPE_FP32;
@@ -462,8 +467,8 @@ int spsattn_decode_fwd(const void* q, int nq, float* out, const spsattn_segment*
                        float sm_scale, void* workspace, size_t workspace_bytes, int* device_status,
                        void* stream) {
   (void)device_status;
-  return decode_impl(q, nq, out, SPSATTN_DTYPE_FP32, segs, n_segments, extras, n_extras, nullptr, S, H, D,
-                     dtype, sm_scale, workspace, workspace_bytes, stream);
+  return decode_impl(q, nq, out, SPSATTN_DTYPE_FP32, segs, n_segments, extras, n_extras, nullptr, false, S, H,
+                     D, dtype, sm_scale, workspace, workspace_bytes, stream);
 }
 
 int spsattn_decode_step(const void* q, int nq, void* out, int out_dtype, const spsattn_segment* segs,
@@ -471,7 +476,7 @@ int spsattn_decode_step(const void* q, int nq, void* out, int out_dtype, const s
                         const spsattn_kv_append* append, int S, int H, int D, int dtype, float sm_scale,
                         void* workspace, size_t workspace_bytes, int* device_status, void* stream) {
   (void)device_status;
-  return decode_impl(q, nq, out, out_dtype, segs, n_segments, extras, n_extras, append, S, H, D, dtype,
+  return decode_impl(q, nq, out, out_dtype, segs, n_segments, extras, n_extras, append, true, S, H, D, dtype,
                      sm_scale, workspace, workspace_bytes, stream);
 }
 

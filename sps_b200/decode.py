@@ -59,6 +59,24 @@ def _segment_scan_len(seg: KVSegment) -> int:
     return max(1, min(max_t, cap))
 
 
+_step_ws: dict = {}
+
+
+def _step_workspace(device, stream_handle: int, nbytes: int) -> Tensor:
+    """Zeroed workspace of the single-launch decode, one per (device, stream): the kernel leaves its
+    completion tickets at zero, and calls on one stream are ordered, so the buffer is cleared only
+    when it is (re)allocated.  A buffer of another size starts over: the tickets sit at its end."""
+    if torch.cuda.is_current_stream_capturing():
+        # memory of a graph's private pool must not outlive the capture in this cache
+        return torch.zeros(nbytes, dtype=torch.uint8, device=device)
+    key = (device.index, stream_handle)
+    ws = _step_ws.get(key)
+    if ws is None or ws.numel() != nbytes:
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _step_ws[key] = ws
+    return ws
+
+
 def _lengths_i64(lengths: Tensor, device) -> Tensor:
     if lengths.device != device:
         raise RuntimeError("Segment lengths must live on the same device as query")
@@ -134,14 +152,15 @@ def decode_attention(
         keep += [ek, ev]
         ex_arr[i].k, ex_arr[i].v, ex_arr[i].query_mask = ek.data_ptr(), ev.data_ptr(), int(qm)
     out = torch.empty((S, nq, H, D), device=dev, dtype=torch.float32)
-    ws_bytes = lib.spsattn_decode_workspace_bytes(S, H, D, nq, seg_arr, n_seg)
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    ws_bytes = lib.spsattn_decode_step_workspace_bytes(S, H, D, nq, seg_arr, n_seg)
     scale = 1.0 / math.sqrt(D) if sm_scale is None else float(sm_scale)
     with torch.cuda.device(dev):
-        rc = lib.spsattn_decode_fwd(q.data_ptr(), nq, out.data_ptr(), seg_arr, n_seg, ex_arr, len(extras),
-                                    S, H, D, dt, scale, ws.data_ptr(), ws_bytes,
-                                    _status(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
-    _lib.check(rc, "spsattn_decode_fwd")
+        stream = torch.cuda.current_stream()
+        ws = _step_workspace(dev, stream.cuda_stream, ws_bytes)
+        rc = lib.spsattn_decode_step(q.data_ptr(), nq, out.data_ptr(), _lib.DTYPE_FP32, seg_arr, n_seg, ex_arr,
+                                     len(extras), None, S, H, D, dt, scale, ws.data_ptr(), ws_bytes,
+                                     _status(dev).data_ptr(), stream.cuda_stream)
+    _lib.check(rc, "spsattn_decode_step")
     return out
 
 

@@ -150,14 +150,18 @@ def _step_case(seed, S, H, D, w, cap, ring_full):
     return case
 
 
-@pytest.mark.parametrize("D,w,ring_full", [(64, 4, True), (64, 4, False), (128, 7, False), (64, 0, False)])
-def test_decode_step_equals_attention_then_update(D, w, ring_full):
+@pytest.mark.parametrize("D,w,ring_full,cap", [(64, 4, True, 37), (64, 4, False, 37), (128, 7, False, 37),
+                                                (64, 0, False, 37), (64, 6, True, 333), (128, 5, False, 700)])
+def test_decode_step_equals_attention_then_update(D, w, ring_full, cap):
     """spsattn_decode_step == spsattn_decode_fwd followed by spsattn_kv_update: same output
-    (fp32 exactly, 16-bit as its rounding), same caches and counters bit for bit."""
+    (fp32 exactly, 16-bit as its rounding), same caches and counters bit for bit.  The larger
+    capacities split a (sequence, head) over several blocks, some of them past the live length;
+    both calls share one workspace, the second relying on the tickets the first left at zero."""
     import sps_b200
     from sps_b200 import _lib
     lib, dev = _lib.load(), _dev()
-    S, H, cap = 9, 3, 37
+    S, H = 9, 3
+    shared_ws = {}
     case = {k: v.to(dev) for k, v in _step_case(11 + D + w, S, H, D, w, cap, ring_full).items()}
     ws_slot, ret_slot = 1, 0
     # separate calls on copies
@@ -201,7 +205,9 @@ def test_decode_step_equals_attention_then_update(D, w, ring_full):
         ap.active = b["active"].data_ptr()
         ap.window_storage, ap.retained_storage, ap.window_tokens = storage, cap, w
         ws_bytes = lib.spsattn_decode_step_workspace_bytes(S, H, D, 2, sarr, n_seg)
-        ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+        if "ws" not in shared_ws:
+            shared_ws["ws"] = torch.zeros(ws_bytes, device=dev, dtype=torch.uint8)   # tickets start at zero
+        ws = shared_ws["ws"]
         out = torch.empty(S, 2, H, D, device=dev,
                           dtype=torch.float32 if out_dtype == _lib.DTYPE_FP32 else torch.bfloat16)
         rc = lib.spsattn_decode_step(b["q"].data_ptr(), 2, out.data_ptr(), out_dtype, sarr, n_seg, ex, 2,
@@ -209,6 +215,8 @@ def test_decode_step_equals_attention_then_update(D, w, ring_full):
                                      ws_bytes, None, torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "decode_step")
         torch.cuda.synchronize()
+        tickets = ws[ws_bytes - 256 * ((4 * (S * H + S) + 255) // 256):]
+        assert int(tickets.count_nonzero()) == 0                        # left zero for the next call
         if out_dtype == _lib.DTYPE_FP32:
             assert torch.equal(out, out_ref)
         else:
