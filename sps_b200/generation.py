@@ -585,3 +585,37 @@ class SPSGenerator:
         torch.where(decode_active.unsqueeze(1), s.logits, g.next_logits, out=g.next_logits)
         g.finished.logical_or_(newly)
         g.step_idx.add_(1)
+
+
+def generator_for(model, *, param_dtype: Optional[torch.dtype] = None) -> SPSGenerator:
+    """Build the engine from an instance of the reference's SPSModel / ReverseSPSModel /
+    DelayedStateModel: its ``config`` supplies the dimensions, its ``state_dict()`` the parameters,
+    its slot indices (sps/inference.py:8-12, reverse_sps/inference.py:58-62) the variant."""
+    cfg = model.config
+    dims = SPSDims(block_size=int(cfg.block_size), vocab_size=int(cfg.vocab_size), n_layer=int(cfg.n_layer),
+                   n_head=int(cfg.n_head), hidden_size=int(cfg.hidden_size),
+                   intermediate_size=int(cfg.intermediate_size), norm_eps=float(cfg.norm_eps),
+                   eos_token_id=int(cfg.eos_token_id), pad_token_id=int(cfg.pad_token_id),
+                   predict_token_id=int(cfg.predict_token_id), window_size=int(cfg.window_size))
+    variant = "sps" if int(getattr(model, "_prediction_slot_index", 0)) == 1 else "reverse_sps"
+    sd = model.state_dict()
+    first = next(iter(sd.values()))
+    if param_dtype is None:
+        param_dtype = torch.bfloat16 if first.dtype == torch.bfloat16 else torch.float32
+    device = first.device if first.is_cuda else torch.device("cuda")
+    return SPSGenerator(sd, dims, variant=variant, device=device, param_dtype=param_dtype)
+
+
+def bind_generate(model, *, param_dtype: Optional[torch.dtype] = None) -> SPSGenerator:
+    """Replace ``model.generate`` (reverse_sps/inference.py:904-951) by the engine, keeping its
+    signature; sampling other than greedy raises instead of falling back.  Returns the engine."""
+    engine = generator_for(model, param_dtype=param_dtype)
+
+    def generate(idx_BxT, max_new_tokens, *, temperature=1.0, top_k=None, top_p=None, do_sample=False,
+                 stop_on_eos=True, forbidden_token_ids=None):
+        del temperature, top_k, top_p
+        return engine.generate(idx_BxT, max_new_tokens, stop_on_eos=stop_on_eos,
+                               forbidden_token_ids=forbidden_token_ids, do_sample=do_sample)
+
+    model.generate = generate
+    return engine

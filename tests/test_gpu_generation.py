@@ -405,3 +405,22 @@ def test_prefill_rejects_what_the_reference_rejects(golden):
         eng.prefill(torch.randint(0, 50, (1, 30)), 8)               # beyond block_size 32
     with pytest.raises(NotImplementedError):
         eng.generate(torch.tensor([[5, 6]]), 2, do_sample=True)
+
+
+def test_bind_generate_replaces_a_reference_style_generate(golden):
+    """generator_for / bind_generate read dims, parameters and the variant off a model object with
+    the reference's attributes and install a generate() with the reference's signature."""
+    import types
+    import sps_b200
+    weights, fields = _golden_model(golden, "rsps")
+    cfg = types.SimpleNamespace(norm_eps=1e-6, **fields)
+    model = types.SimpleNamespace(config=cfg, _prediction_slot_index=0,
+                                  state_dict=lambda: {k: v.to(_dev()) for k, v in weights.items()})
+    eng = sps_b200.bind_generate(model)
+    assert eng.variant == "reverse_sps" and eng.param_dtype == torch.float32
+    idx = torch.from_numpy(golden["model_rsps_padded_idx"])
+    out = model.generate(idx, 3, temperature=1.0, top_k=None, top_p=None, do_sample=False, stop_on_eos=False,
+                         forbidden_token_ids=None)
+    assert torch.equal(out.cpu(), eng.generate(idx, 3, stop_on_eos=False).cpu())
+    with pytest.raises(NotImplementedError):
+        model.generate(idx, 3, do_sample=True)
