@@ -424,3 +424,24 @@ def test_bind_generate_replaces_a_reference_style_generate(golden):
     assert torch.equal(out.cpu(), eng.generate(idx, 3, stop_on_eos=False).cpu())
     with pytest.raises(NotImplementedError):
         model.generate(idx, 3, do_sample=True)
+
+
+def test_left_padded_batch_matches_unpadded_rows(golden):
+    """A row's logits and greedy continuation do not depend on the padding or on the other rows of
+    the batch (tests/models/sps/test_dense_only.py:251-285)."""
+    weights, fields = _golden_model(golden, "sps_w5")
+    eng = _engine(weights, fields, "sps", torch.float32)
+    pad, eos = fields["pad_token_id"], fields["eos_token_id"]
+    prompts = torch.tensor([[pad, pad, 11, eos, 12, 13], [21, 22, 23, 24, 25, 26]])
+    _, batched_logits = eng.prefill(prompts, 4)
+    batched_logits = batched_logits.float().cpu()
+    batched = eng.generate(prompts, 4, stop_on_eos=False).cpu()
+    solo_eng = _engine(weights, fields, "sps", torch.float32)
+    for r in range(2):
+        first = int((prompts[r] != pad).nonzero()[0])
+        single = prompts[r, first:].unsqueeze(0)
+        _, z = solo_eng.prefill(single, 4)
+        torch.testing.assert_close(z.float().cpu()[0], batched_logits[r], atol=2e-3, rtol=2e-3)
+        out = solo_eng.generate(single, 4, stop_on_eos=False).cpu()
+        assert torch.equal(batched[r, :first], torch.full((first,), pad))
+        assert torch.equal(batched[r, first:], out[0]), r

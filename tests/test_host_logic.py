@@ -153,3 +153,37 @@ def test_interval_rule_equals_reference_rule(parity):
             want = orc.visible_mask(n, persistent_parity=parity, temporary_window=w, persistent_window=pw,
                                     mask_flags=flags, docs_row=docs)
             assert np.array_equal(got, want), (n, w, pw, flags)
+
+
+def test_generation_workload_helpers():
+    """The whole-model generation configuration: dims of the benchmark configuration, the speed
+    benchmark's forbidden-id filter, prompt ids below EOS, and the bytes one token step must move."""
+    from sps_b200 import workloads
+    cfg = workloads.GENERATION_CONFIGS["cfg3_xl_generation"]
+    assert (cfg["hidden_size"], cfg["n_layer"], cfg["n_head"], cfg["vocab_size"]) == (2048, 24, 16, 50304)
+    assert cfg["hidden_size"] // cfg["n_head"] == 128 and cfg["block_size"] >= cfg["prompt"] + cfg["new_tokens"]
+    forb = workloads.generation_forbidden_ids(cfg)
+    assert forb == list(range(50257, 50304)) and cfg["pad_token_id"] in forb and cfg["predict_token_id"] in forb
+    assert cfg["eos_token_id"] not in forb
+    p0, p1 = workloads.generation_prompts(cfg, 4, seed=0), workloads.generation_prompts(cfg, 4, seed=1)
+    assert p0.shape == (4, 1024) and p0.max() < cfg["eos_token_id"] and p0.min() >= 0
+    assert (p0 != p1).any()                         # ranks draw different prompts
+    c, i, L = 2048, 8192, 24
+    params = L * (4 * c * c + 3 * c * i) + 50304 * c
+    kv = L * 32 * (1152 + 64) * c * 2
+    assert workloads.generation_step_bytes(cfg, 32, 1152) == 2.0 * (params + kv)
+
+
+def test_generator_refuses_to_work_without_cuda_extension_inputs():
+    """Host-side argument checks of the generation engine that need no GPU."""
+    import pytest as _pytest
+    import torch
+    from sps_b200.generation import (SPSDims, left_padded_position_ids, _validate_left_padded)
+    idx = torch.tensor([[62, 62, 5, 6], [1, 2, 3, 4]])
+    assert left_padded_position_ids(idx, 62).tolist() == [[0, 0, 0, 1], [0, 1, 2, 3]]
+    _validate_left_padded(idx, 62, "prompts")
+    with _pytest.raises(ValueError):
+        _validate_left_padded(torch.tensor([[5, 62, 6]]), 62, "prompts")
+    with _pytest.raises(ValueError):
+        _validate_left_padded(torch.tensor([[62, 62]]), 62, "prompts")
+    assert SPSDims(32, 64, 2, 2, 128, 256).head_dim == 64

@@ -73,3 +73,28 @@ def test_document_ids_known_answer():
     doc = mo.document_idx(idx, eos=63, pad=62)
     assert doc.tolist() == [[0, 1, 2, 2, 3, 3], [0, 0, 0, 0, 0, 0]]
     assert mo.left_padded_positions(idx, 62).tolist() == [[0, 0, 0, 1, 2, 3], [0, 1, 2, 3, 4, 5]]
+
+
+E, P = 63, 62   # EOS and pad ids used below
+
+# (token ids, document ids): the known answers of the reference's tests/core/test_document_idx.py
+DOC_ID_CASES = [
+    ([[1, 2, 3, 4, 5, 6, 7, 8, 9, 10]], [[0] * 10]),                                    # :22-31
+    ([[1, 2, 3, E, 4, 5, 6, 7, 8, 9]], [[0, 0, 0, 0, 1, 1, 1, 1, 1, 1]]),               # :34-43 EOS closes its document
+    ([[1, 2, E, 3, 4, E, 5, 6, 7, 8]], [[0, 0, 0, 1, 1, 1, 2, 2, 2, 2]]),               # :46-55
+    ([[E, 1, 2, 3, 4]], [[0, 1, 1, 1, 1]]),                                             # :58-67 EOS first
+    ([[1, 2, 3, 4, E]], [[0, 0, 0, 0, 0]]),                                             # :69-72 EOS last
+    ([[1, E, E, E, 2, 3]], [[0, 0, 1, 2, 3, 3]]),                                       # :75-84 consecutive EOS
+    ([[1, 2, E, 3, 4, 5, 6, 7, 8, 9], [1, E, 2, 3, E, 4, 5, 6, 7, 8], [1, 2, 3, 4, 5, 6, 7, 8, 9, 10]],
+     [[0, 0, 0, 1, 1, 1, 1, 1, 1, 1], [0, 0, 1, 1, 1, 2, 2, 2, 2, 2], [0] * 10]),       # :87-103 batch
+    ([[P, P, 1, 2, E, 3, 4]], [[0, 1, 2, 2, 2, 3, 3]]),                                 # :105-115 left padding
+]
+
+
+@pytest.mark.parametrize("case", range(len(DOC_ID_CASES)))
+def test_document_ids_match_the_reference_known_answers(case):
+    """Oracle and the package's host function against the literal tensors of the reference's tests."""
+    from sps_b200.generation import left_padded_document_idx
+    idx, want = (torch.tensor(x) for x in DOC_ID_CASES[case])
+    assert torch.equal(mo.document_idx(idx, eos=E, pad=P), want)
+    assert torch.equal(left_padded_document_idx(idx, E, P), want)
