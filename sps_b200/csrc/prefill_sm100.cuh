@@ -78,7 +78,6 @@ struct PrefillCfg {
   static constexpr int kOffBar = kOffP + kPBytes;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;      // barriers + alignment slack
   static constexpr int kBlocksPerSM = (D == 64) ? 3 : 2;
-  static constexpr bool kIncrementalWalk = (D != 64);
 };
 
 struct TileInfo {
@@ -109,6 +108,25 @@ __device__ __forceinline__ TileInfo tile_info(const BlockPlan& bp, int j) {
   return t;
 }
 
+// The tile sequence of a block, precomputed once into shared memory so that every role reads one
+// word per tile instead of re-deriving it from the plan: (k0 << 2) | (stream << 1) | masked.
+// Blocks with more tiles than the table holds fall back to tile_info for the rest.
+constexpr int kTileTable = 128;
+
+__device__ __forceinline__ int pack_tile(const TileInfo& t) {
+  return (t.k0 << 2) | ((t.stream & 1) << 1) | (t.masked ? 1 : 0);
+}
+__device__ __forceinline__ TileInfo unpack_tile(int w) {
+  TileInfo t;
+  t.k0 = w >> 2;             // arithmetic shift: k0 may be negative for a top-aligned first tile
+  t.stream = (w >> 1) & 1;
+  t.masked = (w & 1) != 0;
+  return t;
+}
+__device__ __forceinline__ TileInfo get_tile(const BlockPlan& bp, const int* table, int j) {
+  return j < kTileTable ? unpack_tile(table[j]) : tile_info(bp, j);
+}
+
 // bounded wait executed by a whole converged warp; the outcome is made warp-uniform so that a
 // failure takes all 32 lanes out of their loop together
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
@@ -126,6 +144,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   using Cfg = PrefillCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ BlockPlan s_plan;
+  __shared__ int s_tiles[kTileTable];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
@@ -221,6 +240,9 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   const uint32_t tmem = s_tmem_base;
   const int n_tiles = s_plan.n_tiles;
+  for (int j = tid; j < min(n_tiles, kTileTable); j += kPrefillThreads)
+    s_tiles[j] = pack_tile(tile_info(s_plan, j));
+  __syncthreads();
   if (tid == 0) SPS_TRACE(1, 15);
   volatile int* abort_flag = &s_abort;
   const bool bail = s_abort != 0;
@@ -231,7 +253,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // converged warp, one elected lane issues the copies (tensor-map operands stay uniform)
       {
         auto load_k = [&](int j) {
-          const TileInfo t = tile_info(s_plan, j);
+          const TileInfo t = get_tile(s_plan, s_tiles, j);
           const int st = j % Cfg::kStagesK;
           if (j >= Cfg::kStagesK) {
             if (!warp_wait(bar_k_empty + 8 * st, ((j / Cfg::kStagesK) - 1) & 1, abort_flag, prm.status))
@@ -248,7 +270,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           return true;
         };
         auto load_v = [&](int j) {
-          const TileInfo t = tile_info(s_plan, j);
+          const TileInfo t = get_tile(s_plan, s_tiles, j);
           const int st = j % Cfg::kStagesV;
           if (j >= Cfg::kStagesV) {
             if (!warp_wait(bar_v_empty + 8 * st, ((j / Cfg::kStagesV) - 1) & 1, abort_flag, prm.status))
@@ -372,33 +394,8 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const float c = prm.scale_log2;
       bool ok = true;
 
-      // With registers to spare (head_dim 128: 2 blocks/SM) the tile sequence is walked
-      // incrementally — stream 0 from its top tile downwards, then stream 1 — instead of being
-      // recomputed from the plan for every tile; at head_dim 64 the 96-register budget of three
-      // blocks per SM makes the extra live values cost more in spills than they save.
-      const int n_tiles0 = s_plan.sp[0].ntiles;
-      int cur = 0;
-      int k0 = s_plan.sp[0].top - (kTileN - 1) + kTileN;
-      int kmin_hi = s_plan.sp[0].kmin_hi, kmax_lo = s_plan.sp[0].kmax_lo;
-      bool always_mask = s_plan.sp[0].force_mask || general;
-
       for (int j = 0; j < n_tiles; ++j) {
-        TileInfo t;
-        if constexpr (Cfg::kIncrementalWalk) {
-          if (j == n_tiles0) {
-            cur = 1;
-            k0 = s_plan.sp[1].top - (kTileN - 1) + kTileN;
-            kmin_hi = s_plan.sp[1].kmin_hi;
-            kmax_lo = s_plan.sp[1].kmax_lo;
-            always_mask = s_plan.sp[1].force_mask || general;
-          }
-          k0 -= kTileN;
-          t.stream = s_plan.stream_id[cur];
-          t.k0 = k0;
-          t.masked = always_mask || !(kmin_hi <= k0 && kmax_lo >= k0 + kTileN - 1);
-        } else {
-          t = tile_info(s_plan, j);
-        }
+        const TileInfo t = get_tile(s_plan, s_tiles, j);
         const int sb = j % Cfg::kSBufs;
         if (tid == 0) SPS_TRACE(j, 0);
         if (!mbar_wait(bar_s_full + 8 * sb, (j / Cfg::kSBufs) & 1, abort_flag, prm.status)) {
@@ -424,11 +421,18 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (tid == 0) SPS_TRACE(j, 2);
 
         if (t.masked) {
-          const int cmin = kmin_s[t.stream] - t.k0;
-          const int cmax = kmax_s[t.stream] - t.k0;
+          // the visible columns of this row form an interval: build its bit mask once, then one
+          // bit test per score instead of two comparisons
+          const int cmin = max(kmin_s[t.stream] - t.k0, 0);
+          const int cmax = min(kmax_s[t.stream] - t.k0, kTileN - 1);
+          const unsigned long long vis =
+              cmin > cmax ? 0ull : ((~0ull >> (63 - cmax)) & (~0ull << cmin));
+          const uint32_t vis_lo = (uint32_t)vis, vis_hi = (uint32_t)(vis >> 32);
 #pragma unroll
-          for (int e = 0; e < kTileN; ++e)
-            if (e < cmin || e > cmax) s[e] = -INFINITY;
+          for (int e = 0; e < 32; ++e) {
+            if (!((vis_lo >> e) & 1u)) s[e] = -INFINITY;
+            if (!((vis_hi >> e) & 1u)) s[32 + e] = -INFINITY;
+          }
           if (general) {
             // ids are not monotone: compare this row's id with each key's id (uniform loads)
             uint32_t same[kTileN / 32];
