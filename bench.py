@@ -309,7 +309,7 @@ def run_ours(args):
             "workload": f"{DECODE}: {S} sequences/GPU, cache lengths U[512,4096], ring 64, 16 heads x 64, "
                         "2 queries per sequence, bf16 cache, per layer-step",
             "tokens_per_s": world * S * K / (d_region * 1e-3), "ms_per_step": d_region / K,
-            "algorithmic_mb_per_step": dw.bytes / 1e6, "gpu_launches": 2 * K,
+            "algorithmic_mb_per_step": dw.bytes / 1e6, "gpu_launches": K,   # one launch per step
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
                          "traffic": DECODE_DRAM_BYTES_PER_LAUNCH,
                          "traffic_source": "ncu dram__bytes_read+write of a 32-sequence launch x4 "

@@ -24,7 +24,7 @@ EXPORTS = (
     "spsattn_decode_workspace_bytes", "spsattn_decode_fwd", "spsattn_decode_fwd_noalloc",
     "spsattn_kv_update", "spsattn_fill_decode_caches", "spsattn_rope_cast", "spsattn_debug_visibility",
     "spsattn_decode_step_workspace_bytes", "spsattn_decode_step", "spsattn_qkv_rope_cast",
-    "spsattn_add_rmsnorm", "spsattn_swiglu",
+    "spsattn_add_rmsnorm", "spsattn_swiglu", "spsattn_debug_decode_path",
 )
 
 
@@ -120,6 +120,8 @@ def load() -> C.CDLL:
     lib.spsattn_add_rmsnorm.argtypes = [vp, vp, vp, vp, i32, C.c_longlong, i32, f32, vp]
     lib.spsattn_swiglu.restype = i32
     lib.spsattn_swiglu.argtypes = [vp, vp, i32, C.c_longlong, i32, vp]
+    lib.spsattn_debug_decode_path.restype = i32
+    lib.spsattn_debug_decode_path.argtypes = [i32]
     lib.spsattn_debug_visibility.restype = i32
     lib.spsattn_debug_visibility.argtypes = [vp, vp, i32, i64, i64, i32, i32, i32, i32, i32, i32, vp, sz, vp]
     _lib = lib

@@ -132,6 +132,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_slow(bar, parity, abort_flag, status);
 }
 
+// bounded wait executed by a whole converged warp; the outcome is made warp-uniform so that a
+// failure takes all 32 lanes out of their loop together
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, status);
+  return __all_sync(0xffffffffu, ok);
+}
+
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -256,6 +264,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
         "r"(r[31])
       : "memory");
+}
+// 32 lanes x 2 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_ld2(uint32_t taddr, uint32_t& r0, uint32_t& r1) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];"
+               : "=r"(r0), "=r"(r1)
+               : "r"(taddr)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

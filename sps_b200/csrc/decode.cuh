@@ -63,6 +63,12 @@ struct DecodeParams {
   int out16;
   float* partial;      // [S*H][n_chunks][nq][D + 2]
   int* tickets;        // [S*H + S] zero before the first launch, left zero; null = separate merge launch
+  // Tensor-core kernel only: records are indexed by slot = (segment, chunk inside the segment),
+  // segment after segment, then one slot for the current-token entries.
+  int seg_chunks[kMaxSegments];   // 0 for the short segments of small_segs
+  int extras_slot;     // slot of the current-token entries and the short segments, -1 when none
+  uint32_t small_segs; // bit x: segment x is short and handled with the entries, on the CUDA cores
+  int* status;         // bounded-wait failures are reported here (may be null)
   DecodeAppend app;
   DecodeSeg seg[kMaxSegments];
   const void* extra_k[kMaxExtras];
@@ -127,44 +133,146 @@ __device__ __forceinline__ void merge_records(const DecodeParams& prm, int sh, i
   }
 }
 
+// The same merge for the slot layout of the tensor-core kernel: a slot holds a record iff its
+// chunk starts below the live length of its segment (the slot of the current-token entries and
+// the short segments always does).  `seg_live[x]` = live rows of segment x.
 template <int D, int NQ, bool FP16>
-__global__ void __launch_bounds__(kDecodeThreads, 5)
-decode_split_kernel(const DecodeParams prm) {
+__device__ __forceinline__ void merge_slots(const DecodeParams& prm, int sh, int s, int h,
+                                            const int (&seg_live)[kMaxSegments], int tid, int nthreads) {
+  constexpr int G = 8;
+  const int n_slots = prm.n_chunks;
+  for (int idx = tid; idx < NQ * D; idx += nthreads) {
+    const int qi = idx / D, d = idx % D;
+    const float* rec0 = prm.partial + (size_t)sh * prm.n_chunks * NQ * (D + 2) + qi * (D + 2);
+    float m_run = -1.0e30f, l_run = 0.f, a_run = 0.f;
+    for (int c0 = 0; c0 < n_slots; c0 += G) {
+      float m[G], l[G], a[G];
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        const int c = c0 + j;
+        bool live = false;
+        if (c < n_slots) {
+          if (c == prm.extras_slot) {
+            live = true;
+          } else {
+            int cc = c;
+#pragma unroll
+            for (int x = 0; x < kMaxSegments; ++x) {
+              if (cc >= 0 && cc < prm.seg_chunks[x]) live = cc * prm.chunk_rows < seg_live[x];
+              cc -= prm.seg_chunks[x];
+            }
+          }
+        }
+        const float* rec = rec0 + (size_t)(live ? c : 0) * NQ * (D + 2);
+        m[j] = live ? __ldcg(rec) : -1.0e30f;
+        l[j] = live ? __ldcg(rec + 1) : 0.f;
+        a[j] = live ? __ldcg(rec + 2 + d) : 0.f;
+      }
+      float mx = m_run;
+#pragma unroll
+      for (int j = 0; j < G; ++j) mx = fmaxf(mx, m[j]);
+      const float keep = fast_exp2(m_run - mx);
+      l_run *= keep;
+      a_run *= keep;
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        const float f = fast_exp2(m[j] - mx);
+        l_run = fmaf(l[j], f, l_run);
+        a_run = fmaf(a[j], f, a_run);
+      }
+      m_run = mx;
+    }
+    const float o = l_run > 0.f ? a_run / l_run : 0.f;
+    const size_t off = (((size_t)s * NQ + qi) * prm.H + h) * D + d;
+    if (prm.out16)
+      reinterpret_cast<uint16_t*>(prm.out)[off] = (uint16_t)(pack2<FP16>(o, 0.f) & 0xffffu);
+    else
+      reinterpret_cast<float*>(prm.out)[off] = o;
+  }
+}
+
+// End of a block of a single-launch decode: take the ticket of this (sequence, head); the last
+// block to arrive merges the records, writes the output and applies the cache update.  Every
+// block takes a ticket, also those past the live length, so that all of them have read the
+// counters before any update.  `wrote` = this block stored a record (its stores are fenced).
+template <int D, int NQ, bool FP16, bool SLOTS>
+__device__ __forceinline__ void decode_finish(const DecodeParams& prm, int sh, int s, int h, int n_total,
+                                              const int (&seg_live)[kMaxSegments], long long ring_len,
+                                              long long ring_pos, long long ret_len, bool wrote, int tid,
+                                              int nthreads) {
+  // (the barrier orders the block's record stores before thread 0's fence, which is cumulative)
+  if (wrote) __syncthreads();
+  __shared__ int s_last;
+  if (tid == 0) {
+    if (wrote) __threadfence();
+    const bool last = atomicAdd(&prm.tickets[sh], 1) == (int)gridDim.y - 1;
+    if (last) __threadfence();
+    s_last = last;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if constexpr (SLOTS)
+    merge_slots<D, NQ, FP16>(prm, sh, s, h, seg_live, tid, nthreads);
+  else
+    merge_records<D, NQ, FP16>(prm, sh, s, h, n_total, tid, nthreads);
+  const DecodeAppend& ap = prm.app;
+  const bool append = ap.br_k != nullptr && ap.active[s] != 0;
+  const bool full = ring_len >= ap.window_tokens;
+  if (append) {
+    const long long ins = full ? ring_pos : ring_len;
+    for (int d = tid; d < D; d += nthreads) {
+      const size_t src = (size_t)sh * D + d;
+      if (ap.window_tokens > 0 && ins >= 0 && ins < ap.window_storage) {
+        const size_t dst = ((size_t)sh * ap.window_storage + (size_t)ins) * D + d;
+        ap.nw_k[dst] = ap.k_window[src];
+        ap.nw_v[dst] = ap.v_window[src];
+      }
+      if (ret_len >= 0 && ret_len < ap.retained_storage) {
+        const size_t dst = ((size_t)sh * ap.retained_storage + (size_t)ret_len) * D + d;
+        ap.br_k[dst] = ap.k_retained[src];
+        ap.br_v[dst] = ap.v_retained[src];
+      }
+    }
+  }
+  if (tid == 0) {
+    prm.tickets[sh] = 0;                  // ready for the next launch
+    if (append && ret_len < ap.retained_storage) ap.br_len[sh] = ret_len + 1;
+    if (ap.br_k != nullptr && ap.window_tokens > 0) {
+      // the ring counters belong to the sequence: the last of its heads to get here advances them
+      __threadfence();
+      int* seq_ticket = prm.tickets + (size_t)prm.S * prm.H + s;
+      if (atomicAdd(seq_ticket, 1) == prm.H - 1) {
+        *seq_ticket = 0;
+        if (append) {
+          if (full)
+            ap.nw_pos[s] = (ring_pos + 1) % ap.window_tokens;
+          else
+            ap.nw_len[s] = ring_len + 1;
+        }
+      }
+    }
+  }
+}
+
+// The CUDA-core pass over rows [c_lo, c_hi) of the segments laid end to end (`seg_start` =
+// running sum of their live rows), plus the current-token entries when asked, ending in one
+// record per query at `rec`.  Run by the first kDecodeThreads threads of the block, all of which
+// must call it (it synchronises them on named barrier 2; the other threads stay out).
+template <int D, int NQ, bool FP16>
+__device__ __forceinline__ void cuda_core_chunk(const DecodeParams& prm, int s, int h, int sh,
+                                                const int (&seg_start)[kMaxSegments + 1], int c_lo, int c_hi,
+                                                bool with_extras, float* rec, int tid) {
   constexpr int LPR = D / 8;          // lanes per row
   constexpr int RPI = 32 / LPR;       // rows per warp load instruction
   constexpr int U = kDecodeUnroll;
   constexpr int STEP = 4 * RPI * U;   // rows per block step
   static_assert(D % 8 == 0 && 32 % LPR == 0, "head_dim");
-
-  const int sh = blockIdx.x;
-  const int s = sh / prm.H, h = sh % prm.H;
-  // highest chunk first: blocks past the live length retire at once, at the start of the launch
-  const int chunk = (int)gridDim.y - 1 - (int)blockIdx.y;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warp = (tid >> 5) & 3, lane = tid & 31;
   const int g = lane / LPR;           // row inside a load instruction
   const int dl = (lane % LPR) * 8;    // first of this lane's 8 dims
-
-  int seg_start[kMaxSegments + 1];
-  seg_start[0] = 0;
-#pragma unroll
-  for (int x = 0; x < kMaxSegments; ++x)
-    seg_start[x + 1] = seg_start[x] + (x < prm.n_segments ? live_rows(prm.seg[x], s, h, prm.H) : 0);
-  const int n_total = seg_start[kMaxSegments];
-  const int c_lo = chunk * prm.chunk_rows;
-  const bool dead = chunk > 0 && c_lo >= n_total;
-  if (dead && prm.tickets == nullptr) return;
-  const int c_hi = min(c_lo + prm.chunk_rows, n_total);
-  // the counters as they are before this step's update (any block may be the one that applies it)
-  long long ring_len = 0, ring_pos = 0, ret_len = 0;
-  if (prm.app.br_len != nullptr) {
-    ret_len = prm.app.br_len[(size_t)s * prm.H + h];
-    if (prm.app.window_tokens > 0) {
-      ring_len = prm.app.nw_len[s];
-      ring_pos = prm.app.nw_pos[s];
-    }
-  }
-
-  if (!dead) {   // blocks past the live length only take their ticket below
+  const bool worker = tid < kDecodeThreads;
+  __shared__ float s_m[4][NQ], s_l[4][NQ], s_acc[4][NQ][D];
+  if (worker) {
     // queries, pre-scaled so scores are in the log2 domain
     float q[NQ][8];
 #pragma unroll
@@ -269,7 +377,7 @@ decode_split_kernel(const DecodeParams prm) {
       for (int r = lo + warp * RPI + g; r - (warp * RPI + g) < hi; r += STEP)
         process(kb, vb, sg.row_stride, r, hi, sg.query_mask);
     }
-    if (chunk == 0 && warp == 0) {
+    if (with_extras && warp == 0) {
       // the current-token entries: one row each, handled by lane group 0 of warp 0
       for (int e = 0; e < prm.n_extras; ++e) {
         const uint16_t* kb = reinterpret_cast<const uint16_t*>(prm.extra_k[e]) + (size_t)sh * D;
@@ -296,7 +404,6 @@ decode_split_kernel(const DecodeParams prm) {
         m_run[qi] = mx;
       }
     }
-    __shared__ float s_m[4][NQ], s_l[4][NQ], s_acc[4][NQ][D];
     if (g == 0) {
 #pragma unroll
       for (int qi = 0; qi < NQ; ++qi) {
@@ -308,8 +415,9 @@ decode_split_kernel(const DecodeParams prm) {
         for (int x = 0; x < 8; ++x) s_acc[warp][qi][dl + x] = acc[qi][x];
       }
     }
-    __syncthreads();
-    float* rec = prm.partial + ((size_t)sh * prm.n_chunks + chunk) * NQ * (D + 2);
+  }
+  if (worker) asm volatile("bar.sync 2, %0;" ::"n"(kDecodeThreads) : "memory");
+  if (worker) {
     for (int idx = tid; idx < NQ * D; idx += kDecodeThreads) {
       const int qi = idx / D, d = idx % D;
       float mx = s_m[0][qi];
@@ -329,59 +437,48 @@ decode_split_kernel(const DecodeParams prm) {
       }
     }
   }
+}
+
+template <int D, int NQ, bool FP16>
+__global__ void __launch_bounds__(kDecodeThreads, 5)
+decode_split_kernel(const DecodeParams prm) {
+  const int sh = blockIdx.x;
+  const int s = sh / prm.H, h = sh % prm.H;
+  // highest chunk first: blocks past the live length retire at once, at the start of the launch
+  const int chunk = (int)gridDim.y - 1 - (int)blockIdx.y;
+  const int tid = threadIdx.x;
+
+  int seg_start[kMaxSegments + 1];
+  seg_start[0] = 0;
+#pragma unroll
+  for (int x = 0; x < kMaxSegments; ++x)
+    seg_start[x + 1] = seg_start[x] + (x < prm.n_segments ? live_rows(prm.seg[x], s, h, prm.H) : 0);
+  const int n_total = seg_start[kMaxSegments];
+  const int c_lo = chunk * prm.chunk_rows;
+  const bool dead = chunk > 0 && c_lo >= n_total;
+  if (dead && prm.tickets == nullptr) return;
+  const int c_hi = min(c_lo + prm.chunk_rows, n_total);
+  // the counters as they are before this step's update (any block may be the one that applies it)
+  long long ring_len = 0, ring_pos = 0, ret_len = 0;
+  if (prm.app.br_len != nullptr) {
+    ret_len = prm.app.br_len[(size_t)s * prm.H + h];
+    if (prm.app.window_tokens > 0) {
+      ring_len = prm.app.nw_len[s];
+      ring_pos = prm.app.nw_pos[s];
+    }
+  }
+
+  if (!dead) {   // blocks past the live length only take their ticket below
+    float* rec = prm.partial + ((size_t)sh * prm.n_chunks + chunk) * NQ * (D + 2);
+    cuda_core_chunk<D, NQ, FP16>(prm, s, h, sh, seg_start, c_lo, c_hi, chunk == 0, rec, tid);
+  }
 
   if (prm.tickets == nullptr) return;     // a separate launch merges
-  // Last block of this (sequence, head) to finish merges.  Every block takes a ticket, also
-  // those past the live length, so that all of them have read the counters before any update.
-  // (the barrier orders the block's record stores before thread 0's fence, which is cumulative)
-  if (!dead) __syncthreads();
-  __shared__ int s_last;
-  if (tid == 0) {
-    if (!dead) __threadfence();
-    const bool last = atomicAdd(&prm.tickets[sh], 1) == (int)gridDim.y - 1;
-    if (last) __threadfence();
-    s_last = last;
-  }
-  __syncthreads();
-  if (!s_last) return;
-  merge_records<D, NQ, FP16>(prm, sh, s, h, n_total, tid, kDecodeThreads);
-  const DecodeAppend& ap = prm.app;
-  const bool append = ap.br_k != nullptr && ap.active[s] != 0;
-  const bool full = ring_len >= ap.window_tokens;
-  if (append) {
-    const long long ins = full ? ring_pos : ring_len;
-    for (int d = tid; d < D; d += kDecodeThreads) {
-      const size_t src = (size_t)sh * D + d;
-      if (ap.window_tokens > 0 && ins >= 0 && ins < ap.window_storage) {
-        const size_t dst = ((size_t)sh * ap.window_storage + (size_t)ins) * D + d;
-        ap.nw_k[dst] = ap.k_window[src];
-        ap.nw_v[dst] = ap.v_window[src];
-      }
-      if (ret_len >= 0 && ret_len < ap.retained_storage) {
-        const size_t dst = ((size_t)sh * ap.retained_storage + (size_t)ret_len) * D + d;
-        ap.br_k[dst] = ap.k_retained[src];
-        ap.br_v[dst] = ap.v_retained[src];
-      }
-    }
-  }
-  if (tid == 0) {
-    prm.tickets[sh] = 0;                  // ready for the next launch
-    if (append && ret_len < ap.retained_storage) ap.br_len[sh] = ret_len + 1;
-    if (ap.br_k != nullptr && ap.window_tokens > 0) {
-      // the ring counters belong to the sequence: the last of its heads to get here advances them
-      __threadfence();
-      int* seq_ticket = prm.tickets + (size_t)prm.S * prm.H + s;
-      if (atomicAdd(seq_ticket, 1) == prm.H - 1) {
-        *seq_ticket = 0;
-        if (append) {
-          if (full)
-            ap.nw_pos[s] = (ring_pos + 1) % ap.window_tokens;
-          else
-            ap.nw_len[s] = ring_len + 1;
-        }
-      }
-    }
-  }
+  int seg_live[kMaxSegments];
+#pragma unroll
+  for (int x = 0; x < kMaxSegments; ++x) seg_live[x] = seg_start[x + 1] - seg_start[x];
+  decode_finish<D, NQ, FP16, false>(prm, sh, s, h, n_total, seg_live, ring_len, ring_pos, ret_len, !dead,
+                                    tid, kDecodeThreads);
 }
 
 // Separate merge launch for callers whose workspace carries no tickets: one block of D threads

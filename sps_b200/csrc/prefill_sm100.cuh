@@ -127,14 +127,6 @@ __device__ __forceinline__ TileInfo get_tile(const BlockPlan& bp, const int* tab
   return j < kTileTable ? unpack_tile(table[j]) : tile_info(bp, j);
 }
 
-// bounded wait executed by a whole converged warp; the outcome is made warp-uniform so that a
-// failure takes all 32 lanes out of their loop together
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status) {
-  const bool ok = mbar_wait(bar, parity, abort_flag, status);
-  return __all_sync(0xffffffffu, ok);
-}
-
 constexpr float kRescaleLog2 = 8.0f;
 
 template <int D, bool FP16>

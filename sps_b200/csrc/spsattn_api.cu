@@ -6,11 +6,13 @@
 #include <stdint.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "../../include/spsattn.h"
 #include "cache_fill.cuh"
 #include "decode.cuh"
+#include "decode_sm100.cuh"
 #include "kv_update.cuh"
 #include "model_glue.cuh"
 #include "prefill_aux.cuh"
@@ -173,6 +175,103 @@ template <int D>
 static int launch_decode_d(const DecodeParams& prm, int nq, bool fp16, cudaStream_t st) {
   if (nq == 1) return fp16 ? launch_decode<D, 1, true>(prm, st) : launch_decode<D, 1, false>(prm, st);
   return fp16 ? launch_decode<D, 2, true>(prm, st) : launch_decode<D, 2, false>(prm, st);
+}
+
+// ---- tensor-core decode (decode_sm100.cuh): slot layout and launch
+constexpr int kTcSmallRows = 128;   // segments up to this many rows go with the current-token entries
+std::atomic<int> g_decode_path{0};   // 0 auto, 1 CUDA-core kernel, 2 tensor-core kernel
+
+int tc_chunk_rows(int S, int H, const spsattn_segment* segs, int n_segments) {
+  // A block pays a fixed start-up (tensor memory, barriers, zeroed operand tiles) and a block
+  // past the live length still occupies a shared-memory slot while it takes its ticket: one
+  // chunk per segment when there are enough (sequence, head) pairs to fill the machine, halved
+  // until there are.
+  long long longest = kTcTile;
+  for (int x = 0; x < n_segments; ++x)
+    if (segs[x].max_rows > longest) longest = segs[x].max_rows;
+  long long chunk = (longest + kTcTile - 1) / kTcTile * kTcTile;
+  while (chunk > kTcTile) {
+    long long blocks = 0;
+    for (int x = 0; x < n_segments; ++x)
+      if (segs[x].max_rows > kTcSmallRows) blocks += (segs[x].max_rows + chunk - 1) / chunk;
+    if ((long long)S * H * blocks >= 148LL * 4) break;
+    chunk = (chunk / 2 + kTcTile - 1) / kTcTile * kTcTile;
+  }
+  return (int)chunk;
+}
+
+bool tc_supported(const spsattn_segment* segs, int n_segments, int D) {
+  if (D != 64 && D != 128) return false;
+  for (int x = 0; x < n_segments; ++x)
+    if (segs[x].seq_offset != nullptr) return false;   // packed caches have no single tensor map
+  return true;
+}
+
+int tc_slots(const spsattn_segment* segs, int n_segments, int n_extras, int chunk, int* seg_chunks,
+             uint32_t* small_segs) {
+  int total = 0;
+  uint32_t small = 0;
+  for (int x = 0; x < kMaxSegments; ++x) {
+    const int rows = (x < n_segments && segs[x].max_rows > 0) ? segs[x].max_rows : 0;
+    int c = (rows + chunk - 1) / chunk;
+    if (rows > 0 && rows <= kTcSmallRows) {
+      small |= 1u << x;
+      c = 0;
+    }
+    if (seg_chunks) seg_chunks[x] = c;
+    total += c;
+  }
+  if (small_segs) *small_segs = small;
+  if (n_extras > 0 || small != 0) ++total;
+  return total > 0 ? total : 1;
+}
+
+int encode_cache_map(CUtensorMap* tm, const void* ptr, const spsattn_segment& sg, int S, int H, int D,
+                            int dtype) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return SPSATTN_ERR_DRIVER;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)sg.max_rows, (cuuint64_t)H, (cuuint64_t)S};
+  cuuint64_t strides[3] = {(cuuint64_t)sg.row_stride * 2, (cuuint64_t)sg.head_stride * 2,
+                           (cuuint64_t)sg.seq_stride * 2};
+  // a degenerate extent (one head or one sequence) may carry any stride: keep it encodable
+  if (H == 1) strides[1] = strides[0] * (cuuint64_t)sg.max_rows;
+  if (S == 1) strides[2] = strides[1] * (cuuint64_t)H;
+  cuuint32_t box[4] = {64, (cuuint32_t)kTcTile, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, dtype == SPSATTN_DTYPE_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                   4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+template <int D, int NQ, bool FP16>
+int launch_decode_tc(const DecodeMaps& maps, const DecodeParams& prm, cudaStream_t st) {
+  using Cfg = DecodeTcCfg<D>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(decode_tc_kernel<D, NQ, FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return (int)attr_err;
+  // one block per chunk of a long segment; the record slot of the current-token entries and short
+  // segments has no block of its own (slot 0's block fills it)
+  int blocks_y = 0;
+  for (int x = 0; x < kMaxSegments; ++x) blocks_y += prm.seg_chunks[x];
+  if (blocks_y < 1) blocks_y = 1;
+  dim3 grid((unsigned)(prm.S * prm.H), (unsigned)blocks_y);
+  decode_tc_kernel<D, NQ, FP16><<<grid, kTcThreads, Cfg::kSmemBytes, st>>>(maps, prm);
+  return (int)cudaGetLastError();
+}
+
+template <int D>
+int launch_decode_tc_d(const DecodeMaps& maps, const DecodeParams& prm, int nq, bool fp16,
+                              cudaStream_t st) {
+  if (nq == 1)
+    return fp16 ? launch_decode_tc<D, 1, true>(maps, prm, st) : launch_decode_tc<D, 1, false>(maps, prm, st);
+  return fp16 ? launch_decode_tc<D, 2, true>(maps, prm, st) : launch_decode_tc<D, 2, false>(maps, prm, st);
 }
 
 }  // namespace
@@ -340,6 +439,10 @@ static size_t decode_records_bytes(int S, int H, int D, int nq, const spsattn_se
   const int chunk = decode_chunk_rows(S, H, rows);
   long long n_chunks = (rows + chunk - 1) / chunk;
   if (n_chunks < 1) n_chunks = 1;
+  // the tensor-core kernel indexes its records by (segment, chunk) plus one slot for the
+  // current-token entries: room for whichever layout the call ends up using
+  const long long slots = tc_slots(segs, n_segments, kMaxExtras, tc_chunk_rows(S, H, segs, n_segments), nullptr, nullptr);
+  if (slots > n_chunks) n_chunks = slots;
   return align_up((size_t)S * H * n_chunks * nq * (D + 2) * sizeof(float), 256);
 }
 
@@ -359,7 +462,8 @@ size_t spsattn_decode_step_workspace_bytes(int S, int H, int D, int nq, const sp
 static int decode_impl(const void* q, int nq, void* out, int out_dtype, const spsattn_segment* segs,
                        int n_segments, const spsattn_extra* extras, int n_extras,
                        const spsattn_kv_append* append, bool single_launch, int S, int H, int D, int dtype,
-                       float sm_scale, void* workspace, size_t workspace_bytes, void* stream) {
+                       float sm_scale, void* workspace, size_t workspace_bytes, int* device_status,
+                       void* stream) {
   if (!q || !out) return SPSATTN_ERR_ARG;
   if (nq != 1 && nq != 2) return SPSATTN_ERR_ARG;
   if (S <= 0 || H <= 0) return SPSATTN_ERR_ARG;
@@ -401,13 +505,28 @@ static int decode_impl(const void* q, int nq, void* out, int out_dtype, const sp
     prm.extra_mask[e] = extras[e].query_mask;
   }
   const long long rows = decode_max_rows(segs, n_segments);
-  prm.chunk_rows = decode_chunk_rows(S, H, rows);
-  long long n_chunks = (rows + prm.chunk_rows - 1) / prm.chunk_rows;
-  if (n_chunks < 1) n_chunks = 1;
+  const int path = g_decode_path.load();
+  const bool tc_ok = single_launch && tc_supported(segs, n_segments, D);
+  if (path == 2 && !tc_ok) return SPSATTN_ERR_ARG;
+  // automatic choice: head_dim 64, where two well-fed blocks per SM reach 85 % of the copy
+  // bandwidth against 78 % for the CUDA-core kernel; at head_dim 128 (one K/V stage per block)
+  // the CUDA-core kernel is still ahead (75 us against 84 us at the generation shape)
+  const bool use_tc = tc_ok && (path == 2 || (path == 0 && D == 64));
+  long long n_chunks;
+  if (use_tc) {
+    prm.chunk_rows = tc_chunk_rows(S, H, segs, n_segments);
+    n_chunks = tc_slots(segs, n_segments, n_extras, prm.chunk_rows, prm.seg_chunks, &prm.small_segs);
+    prm.extras_slot = (n_extras > 0 || prm.small_segs != 0) ? (int)n_chunks - 1 : -1;
+  } else {
+    prm.chunk_rows = decode_chunk_rows(S, H, rows);
+    n_chunks = (rows + prm.chunk_rows - 1) / prm.chunk_rows;
+    if (n_chunks < 1) n_chunks = 1;
+    prm.extras_slot = -1;
+  }
   if (n_chunks > 65535) return SPSATTN_ERR_TOO_LARGE;
   prm.n_chunks = (int)n_chunks;
   const size_t raw = (size_t)S * H * n_chunks * nq * (D + 2) * sizeof(float);
-  const size_t records = align_up(raw, 256);
+  const size_t records = single_launch ? decode_records_bytes(S, H, D, nq, segs, n_segments) : align_up(raw, 256);
   const size_t need = single_launch ? records + decode_ticket_bytes(S, H) : raw;
   if (!workspace || workspace_bytes < need) return SPSATTN_ERR_WORKSPACE;
   if (append && !single_launch) return SPSATTN_ERR_ARG;
@@ -450,8 +569,21 @@ static int decode_impl(const void* q, int nq, void* out, int out_dtype, const sp
   prm.H = H;
   prm.nq = nq;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
+  prm.status = device_status;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool fp16 = dtype == SPSATTN_DTYPE_FP16;
+  if (use_tc) {
+    DecodeMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    for (int x = 0; x < n_segments; ++x) {
+      if (prm.seg_chunks[x] == 0) continue;
+      int rc = encode_cache_map(&maps.k[x], segs[x].k, segs[x], S, H, D, dtype);
+      if (rc == 0) rc = encode_cache_map(&maps.v[x], segs[x].v, segs[x], S, H, D, dtype);
+      if (rc != 0) return rc;
+    }
+    return D == 64 ? launch_decode_tc_d<64>(maps, prm, nq, fp16, st)
+                   : launch_decode_tc_d<128>(maps, prm, nq, fp16, st);
+  }
   switch (D) {
     case 8: return launch_decode_d<8>(prm, nq, fp16, st);
     case 16: return launch_decode_d<16>(prm, nq, fp16, st);
@@ -466,18 +598,22 @@ int spsattn_decode_fwd(const void* q, int nq, float* out, const spsattn_segment*
                        const spsattn_extra* extras, int n_extras, int S, int H, int D, int dtype,
                        float sm_scale, void* workspace, size_t workspace_bytes, int* device_status,
                        void* stream) {
-  (void)device_status;
   return decode_impl(q, nq, out, SPSATTN_DTYPE_FP32, segs, n_segments, extras, n_extras, nullptr, false, S, H,
-                     D, dtype, sm_scale, workspace, workspace_bytes, stream);
+                     D, dtype, sm_scale, workspace, workspace_bytes, device_status, stream);
 }
 
 int spsattn_decode_step(const void* q, int nq, void* out, int out_dtype, const spsattn_segment* segs,
                         int n_segments, const spsattn_extra* extras, int n_extras,
                         const spsattn_kv_append* append, int S, int H, int D, int dtype, float sm_scale,
                         void* workspace, size_t workspace_bytes, int* device_status, void* stream) {
-  (void)device_status;
   return decode_impl(q, nq, out, out_dtype, segs, n_segments, extras, n_extras, append, true, S, H, D, dtype,
-                     sm_scale, workspace, workspace_bytes, stream);
+                     sm_scale, workspace, workspace_bytes, device_status, stream);
+}
+
+int spsattn_debug_decode_path(int path) {
+  if (path < 0 || path > 2) return SPSATTN_ERR_ARG;
+  g_decode_path.store(path);
+  return 0;
 }
 
 // ------------------------------------------------------------------------------------ rope + cast
