@@ -37,8 +37,8 @@ PREFILL_FULL_WINDOW = "cfg4_full_window"
 GENERATION = "cfg3_xl_generation"
 # DRAM traffic per full-size launch, from ncu captures of a smaller case scaled by the units
 # processed (traffic is proportional to batch rows / sequences)
-PREFILL_DRAM_BYTES_PER_LAUNCH = 2 * (151.4e6 + 34.0e6)
-DECODE_DRAM_BYTES_PER_LAUNCH = 4 * (323.7e6 + 6.4e6)
+PREFILL_DRAM_BYTES_PER_LAUNCH = 2 * (151.4e6 + 33.3e6)
+DECODE_DRAM_BYTES_PER_LAUNCH = 4 * (332.2e6 + 6.2e6)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -313,7 +313,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
                          "traffic": DECODE_DRAM_BYTES_PER_LAUNCH,
                          "traffic_source": "ncu dram__bytes_read+write of a 32-sequence launch x4 "
-                                           "(profiles/decode_split_d64_cfg2_32seq.md)",
+                                           "(profiles/decode_tc_d64_cfg2_32seq.md)",
                          "peak_source": f"{peak_kind} copy bandwidth", "launch_ms": d_launch},
         }
         sps_b200.check_device_status(device)
@@ -533,9 +533,15 @@ def main():
     ap.add_argument("--skip-full-window", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-generation", action="store_true")
+    ap.add_argument("--decode-path", choices=["auto", "cuda-core", "tensor-core"], default="auto",
+                    help="decode kernel behind the decode step (auto: tensor cores at head_dim 64)")
     ap.add_argument("--new-tokens", type=int, default=None, help="generation cases: tokens to generate")
     ap.add_argument("--runs", type=int, default=3, help="generation cases: timed repetitions")
     args = ap.parse_args()
+    if args.decode_path != "auto" and args.impl == "ours":
+        from sps_b200 import _lib
+        _lib.check(_lib.load().spsattn_debug_decode_path({"cuda-core": 1, "tensor-core": 2}[args.decode_path]),
+                   "spsattn_debug_decode_path")
     if args.impl == "reference":
         run_reference(args)
     elif args.case != "full":
