@@ -9,8 +9,8 @@
 // One block per (sequence, head, slot); a slot is a chunk of one long segment (chunk_rows keys,
 // tiles of 128), or the one slot of the current-token entries and the short segments (a ring of
 // a few dozen rows), which the CUDA-core routine of decode.cuh handles.  Per tile:
-//   producer warp   TMA: K tile [128 keys x D] and V tile [128 keys x D] -> shared memory
-//                   (128-byte swizzle, two or three stages each)
+//   producer warp   TMA: K tile [128 keys x D] and V tile [128 keys x D] -> shared memory, as
+//                   units of [128 keys x 64 dims] through one ring (128-byte swizzle)
 //   MMA warp        S^T[128 keys x 16]  = K[128 x D] . Qpad[16 x D]^T        (queries padded to 16)
 //                   O[64 x D]          += P[64 x 128 keys] . V[128 keys x D]  (rows >= nq of P are 0)
 //   4 softmax warps thread t owns key t of the tile: reads its nq scores from TMEM, masks rows
@@ -39,14 +39,17 @@ constexpr float kTcRescaleLog2 = 8.0f;
 
 template <int D>
 struct DecodeTcCfg {
-  // Two blocks per SM either way, so that the start-up and the record of one overlap the
-  // streaming of the other: head_dim 64 has room for two K/V stages and two P buffers per block,
-  // head_dim 128 for one of each (measured: 84 us against 107 us for one block per SM with three
-  // stages at 32 sequences x 16 heads x 1216 rows).
-  static constexpr int kStages = D == 64 ? 2 : 1;
+  // K and V tiles travel as units of [128 keys x 64 dims] (16 KB, one TMA box, one 128-byte
+  // swizzled block the MMA reads as is): a tile is one K unit and one V unit at head_dim 64, two
+  // and two at 128, streamed in that order through one ring of units.  A unit is released as
+  // soon as the MMAs that read it are done, so the ring stays full whatever the head dim.
+  // Two blocks per SM either way (the start-up and the record of one overlap the streaming of
+  // the other): ring of 4 units + two P buffers at head_dim 64, 5 units + one P buffer at 128.
+  static constexpr int kUnit = kTcTile * 128;
+  static constexpr int kUnitsPerOperand = D / 64;
+  static constexpr int kUnitsPerTile = 2 * kUnitsPerOperand;
+  static constexpr int kRing = D == 64 ? 4 : 5;
   static constexpr int kPBufs = D == 64 ? 2 : 1;
-  static constexpr int kKVSub = kTcTile * 128;            // one 64-wide sub-tile: 128 rows x 128 B
-  static constexpr int kKVBytes = kTcTile * D * 2;
   static constexpr int kQSub = kTcQPad * 128;             // 16 rows x 128 B
   static constexpr int kQBytes = 4096;                    // reserved (D = 128 needs 4096)
   static constexpr int kPRows = 64;                        // M of the second product (nq rows used)
@@ -54,9 +57,8 @@ struct DecodeTcCfg {
   static constexpr int kPBuf = 2 * kPSub;                  // one P tile: [64 rows x 128 keys]
   static constexpr int kPBytes = kPBufs * kPBuf;
   static constexpr int kOffQ = 0;
-  static constexpr int kOffK = kQBytes;
-  static constexpr int kOffV = kOffK + kStages * kKVBytes;
-  static constexpr int kOffP = kOffV + kStages * kKVBytes;
+  static constexpr int kOffRing = kQBytes;
+  static constexpr int kOffP = kOffRing + kRing * kUnit;
   static constexpr int kOffBar = kOffP + kPBytes;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;  // barriers + alignment slack
   static constexpr int kColS = 0;                          // 2 buffers of 16 columns
@@ -139,14 +141,11 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
     // ------------------------------------------------------------ a chunk of one segment
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = smem_base + Cfg::kOffQ;
-    const uint32_t sK = smem_base + Cfg::kOffK;
-    const uint32_t sV = smem_base + Cfg::kOffV;
+    const uint32_t sRing = smem_base + Cfg::kOffRing;
     const uint32_t sP = smem_base + Cfg::kOffP;
     const uint32_t bar0 = smem_base + Cfg::kOffBar;
-    const uint32_t bar_k_full = bar0;          // [kStages]
-    const uint32_t bar_k_empty = bar0 + 32;    // [kStages]
-    const uint32_t bar_v_full = bar0 + 64;     // [kStages]
-    const uint32_t bar_v_empty = bar0 + 96;    // [kStages]
+    const uint32_t bar_full = bar0;            // [kRing] unit landed
+    const uint32_t bar_empty = bar0 + 64;      // [kRing] unit consumed
     const uint32_t bar_s_full = bar0 + 128;    // [2]
     const uint32_t bar_s_free = bar0 + 144;    // [2]
     const uint32_t bar_p_full = bar0 + 160;    // [kPBufs]
@@ -177,11 +176,9 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
     }
     if (warp == 4) {
       if (lane == 0) {
-        for (int x = 0; x < Cfg::kStages; ++x) {
-          mbar_init(bar_k_full + 8 * x, 1);
-          mbar_init(bar_k_empty + 8 * x, 1);
-          mbar_init(bar_v_full + 8 * x, 1);
-          mbar_init(bar_v_empty + 8 * x, 1);
+        for (int x = 0; x < Cfg::kRing; ++x) {
+          mbar_init(bar_full + 8 * x, 1);
+          mbar_init(bar_empty + 8 * x, 1);
         }
         for (int x = 0; x < 2; ++x) {
           mbar_init(bar_s_full + 8 * x, 1);
@@ -210,89 +207,96 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
     if (!bail) {
       if (warp == 4) {
         // -------------------------------------------------------------- TMA producer
-        for (int j = 0; j < n_tiles; ++j) {
-          const int st = j % Cfg::kStages;
-          const int r = row0 + j * kTcTile;
-          if (j >= Cfg::kStages &&
-              !warp_wait(bar_k_empty + 8 * st, ((j / Cfg::kStages) - 1) & 1, abort_flag, prm.status))
+        // unit g of the stream: tile g / kUnitsPerTile; first the K units of the tile, then its V units
+        const int n_units = n_tiles * Cfg::kUnitsPerTile;
+        for (int g = 0; g < n_units; ++g) {
+          const int slot = g % Cfg::kRing;
+          if (g >= Cfg::kRing &&
+              !warp_wait(bar_empty + 8 * slot, ((g / Cfg::kRing) - 1) & 1, abort_flag, prm.status))
             break;
+          const int j = g / Cfg::kUnitsPerTile, w = g % Cfg::kUnitsPerTile;
+          const bool is_v = w >= Cfg::kUnitsPerOperand;
+          const int c = w % Cfg::kUnitsPerOperand;
           if (elect_one()) {
-            mbar_arrive_expect_tx(bar_k_full + 8 * st, Cfg::kKVBytes);
-            for (int c = 0; c < D / 64; ++c)
-              tma_load_4d(sK + st * Cfg::kKVBytes + c * Cfg::kKVSub, &maps.k[seg], bar_k_full + 8 * st,
-                          c * 64, r, h, s);
-          }
-          __syncwarp();
-          if (j >= Cfg::kStages &&
-              !warp_wait(bar_v_empty + 8 * st, ((j / Cfg::kStages) - 1) & 1, abort_flag, prm.status))
-            break;
-          if (elect_one()) {
-            mbar_arrive_expect_tx(bar_v_full + 8 * st, Cfg::kKVBytes);
-            for (int c = 0; c < D / 64; ++c)
-              tma_load_4d(sV + st * Cfg::kKVBytes + c * Cfg::kKVSub, &maps.v[seg], bar_v_full + 8 * st,
-                          c * 64, r, h, s);
+            mbar_arrive_expect_tx(bar_full + 8 * slot, Cfg::kUnit);
+            tma_load_4d(sRing + slot * Cfg::kUnit, is_v ? &maps.v[seg] : &maps.k[seg], bar_full + 8 * slot,
+                        c * 64, row0 + j * kTcTile, h, s);
           }
           __syncwarp();
         }
       } else if (warp == 5) {
         // -------------------------------------------------------------- MMA issuer
         constexpr uint32_t idesc_s = make_idesc_f16(FP16, 128, kTcQPad, false, false);
-        constexpr uint32_t idesc_o = make_idesc_f16(FP16, Cfg::kPRows, D, false, true);
+        constexpr uint32_t idesc_o = make_idesc_f16(FP16, Cfg::kPRows, 64, false, true);
         const uint64_t dq64 = make_smem_desc_sw128(sQ, 16, 1024);
-        const uint64_t dk64 = make_smem_desc_sw128(sK, 16, 1024);
+        const uint64_t dk64 = make_smem_desc_sw128(sRing, 16, 1024);          // unit as K-major A
         const uint64_t dp64 = make_smem_desc_sw128(sP, 16, 1024);
-        const uint64_t dv64 = make_smem_desc_sw128(sV, Cfg::kKVSub, 1024);
+        const uint64_t dv64 = make_smem_desc_sw128(sRing, Cfg::kUnit, 1024);  // unit as MN-major B
         const uint32_t dq_lo = (uint32_t)dq64, dq_hi = (uint32_t)(dq64 >> 32);
         const uint32_t dk_lo = (uint32_t)dk64, dk_hi = (uint32_t)(dk64 >> 32);
         const uint32_t dp_lo = (uint32_t)dp64, dp_hi = (uint32_t)(dp64 >> 32);
         const uint32_t dv_lo = (uint32_t)dv64, dv_hi = (uint32_t)(dv64 >> 32);
+        // scores of tile j: one group of four K steps per K unit, each unit released on its own
         auto issue_s = [&](int j) {
-          const int st = j % Cfg::kStages, sb = j & 1;
+          const int sb = j & 1;
           if (j >= 2 && !warp_wait(bar_s_free + 8 * sb, ((j >> 1) - 1) & 1, abort_flag, prm.status))
             return false;
-          if (!warp_wait(bar_k_full + 8 * st, (j / Cfg::kStages) & 1, abort_flag, prm.status)) return false;
-          tc_fence_after();
-          const uint32_t ka0 = dk_lo + ((st * Cfg::kKVBytes) >> 4);
           const uint32_t sd = tmem + Cfg::kColS + sb * kTcQPad;
-          if (elect_one()) {
-            // a K step of 16 elements is 32 bytes inside a 128-byte row; 64 elements per sub-tile
-            umma_ss<false>(sd, ka0, dk_hi, dq_lo, dq_hi, idesc_s);
 #pragma unroll
-            for (int kk = 1; kk < D / 16; ++kk) {
-              const uint32_t ka = ((kk / 4) * Cfg::kKVSub + (kk % 4) * 32) >> 4;
-              const uint32_t qb = ((kk / 4) * Cfg::kQSub + (kk % 4) * 32) >> 4;
-              umma_ss<true>(sd, ka0 + ka, dk_hi, dq_lo + qb, dq_hi, idesc_s);
+          for (int c = 0; c < Cfg::kUnitsPerOperand; ++c) {
+            const int g = j * Cfg::kUnitsPerTile + c, slot = g % Cfg::kRing;
+            if (!warp_wait(bar_full + 8 * slot, (g / Cfg::kRing) & 1, abort_flag, prm.status)) return false;
+            tc_fence_after();
+            const uint32_t ka0 = dk_lo + ((slot * Cfg::kUnit) >> 4);
+            const uint32_t qb0 = dq_lo + ((c * Cfg::kQSub) >> 4);
+            if (elect_one()) {
+              // a K step of 16 elements is 32 bytes inside a 128-byte row
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) {
+                if (c == 0 && kk == 0)
+                  umma_ss<false>(sd, ka0, dk_hi, qb0, dq_hi, idesc_s);
+                else
+                  umma_ss<true>(sd, ka0 + ((kk * 32) >> 4), dk_hi, qb0 + ((kk * 32) >> 4), dq_hi, idesc_s);
+              }
+              umma_commit(bar_empty + 8 * slot);
+              if (c == Cfg::kUnitsPerOperand - 1) umma_commit(bar_s_full + 8 * sb);
             }
-            umma_commit(bar_s_full + 8 * sb);
-            umma_commit(bar_k_empty + 8 * st);
+            __syncwarp();
           }
-          __syncwarp();
           return true;
         };
         bool ok = issue_s(0);
         for (int j = 0; ok && j < n_tiles; ++j) {
           if (j + 1 < n_tiles) ok = issue_s(j + 1);
           if (!ok) break;
-          const int st = j % Cfg::kStages, pb = j % Cfg::kPBufs;
+          const int pb = j % Cfg::kPBufs;
           if (!warp_wait(bar_p_full + 8 * pb, (j / Cfg::kPBufs) & 1, abort_flag, prm.status)) break;
-          if (!warp_wait(bar_v_full + 8 * st, (j / Cfg::kStages) & 1, abort_flag, prm.status)) break;
-          tc_fence_after();
-          const uint32_t vb0 = dv_lo + ((st * Cfg::kKVBytes) >> 4);
-          const uint32_t od = tmem + Cfg::kColO;
-          if (elect_one()) {
-            // P: K-major, two 64-key sub-tiles; V: MN-major, 16 key rows = 2048 bytes per step
+          // output: one 64-column half per V unit, P: K-major, two 64-key sub-tiles; a V unit is
+          // MN-major, 16 key rows = 2048 bytes per K step
 #pragma unroll
-            for (int kk = 0; kk < kTcTile / 16; ++kk) {
-              const uint32_t pa = (pb * Cfg::kPBuf + (kk / 4) * Cfg::kPSub + (kk % 4) * 32) >> 4;
-              if (kk == 0 && j == 0)
-                umma_ss<false>(od, dp_lo + pa, dp_hi, vb0 + ((kk * 2048) >> 4), dv_hi, idesc_o);
-              else
-                umma_ss<true>(od, dp_lo + pa, dp_hi, vb0 + ((kk * 2048) >> 4), dv_hi, idesc_o);
+          for (int c = 0; c < Cfg::kUnitsPerOperand; ++c) {
+            const int g = j * Cfg::kUnitsPerTile + Cfg::kUnitsPerOperand + c, slot = g % Cfg::kRing;
+            if (!warp_wait(bar_full + 8 * slot, (g / Cfg::kRing) & 1, abort_flag, prm.status)) {
+              ok = false;
+              break;
             }
-            umma_commit(bar_pv_done + 8 * pb);
-            umma_commit(bar_v_empty + 8 * st);
+            tc_fence_after();
+            const uint32_t vb0 = dv_lo + ((slot * Cfg::kUnit) >> 4);
+            const uint32_t od = tmem + Cfg::kColO + c * 64;
+            if (elect_one()) {
+#pragma unroll
+              for (int kk = 0; kk < kTcTile / 16; ++kk) {
+                const uint32_t pa = (pb * Cfg::kPBuf + (kk / 4) * Cfg::kPSub + (kk % 4) * 32) >> 4;
+                if (kk == 0 && j == 0)
+                  umma_ss<false>(od, dp_lo + pa, dp_hi, vb0, dv_hi, idesc_o);
+                else
+                  umma_ss<true>(od, dp_lo + pa, dp_hi, vb0 + ((kk * 2048) >> 4), dv_hi, idesc_o);
+              }
+              umma_commit(bar_empty + 8 * slot);
+              if (c == Cfg::kUnitsPerOperand - 1) umma_commit(bar_pv_done + 8 * pb);
+            }
+            __syncwarp();
           }
-          __syncwarp();
         }
       } else {
         // -------------------------------------------------------------- softmax warps
@@ -308,7 +312,7 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
         bool ok = true;
         if (small_owner) small_work();
         for (int j = 0; j < n_tiles; ++j) {
-          const int sb = j & 1, st = j % Cfg::kStages;
+          const int sb = j & 1;
           if (!mbar_wait(bar_s_full + 8 * sb, (j >> 1) & 1, abort_flag, prm.status)) {
             ok = false;
             break;
@@ -404,18 +408,17 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
           }
           if ((j + 1) * kTcTile > rows) {
             // last tile of the chunk: rows past the live length must not reach the product
-            if (!mbar_wait(bar_v_full + 8 * st, (j / Cfg::kStages) & 1, abort_flag, prm.status)) {
-              ok = false;
-              break;
-            }
-            if (!valid) {
 #pragma unroll
-              for (int c = 0; c < D / 64; ++c) {
-                uint4* vrow = reinterpret_cast<uint4*>(gen + Cfg::kOffV + st * Cfg::kKVBytes + c * Cfg::kKVSub + t * 128);
+            for (int c = 0; c < Cfg::kUnitsPerOperand; ++c) {
+              const int g = j * Cfg::kUnitsPerTile + Cfg::kUnitsPerOperand + c, slot = g % Cfg::kRing;
+              if (!mbar_wait(bar_full + 8 * slot, (g / Cfg::kRing) & 1, abort_flag, prm.status)) ok = false;
+              if (ok && !valid) {
+                uint4* vrow = reinterpret_cast<uint4*>(gen + Cfg::kOffRing + slot * Cfg::kUnit + t * 128);
 #pragma unroll
                 for (int x = 0; x < 8; ++x) vrow[x] = make_uint4(0, 0, 0, 0);
               }
             }
+            if (!ok) break;
           }
           fence_proxy_async_smem();
           tc_fence_before();

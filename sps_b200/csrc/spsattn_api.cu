@@ -508,9 +508,10 @@ static int decode_impl(const void* q, int nq, void* out, int out_dtype, const sp
   const int path = g_decode_path.load();
   const bool tc_ok = single_launch && tc_supported(segs, n_segments, D);
   if (path == 2 && !tc_ok) return SPSATTN_ERR_ARG;
-  // automatic choice: head_dim 64, where two well-fed blocks per SM reach 85 % of the copy
-  // bandwidth against 78 % for the CUDA-core kernel; at head_dim 128 (one K/V stage per block)
-  // the CUDA-core kernel is still ahead (75 us against 84 us at the generation shape)
+  // automatic choice: head_dim 64, where the tensor-core kernel reaches 85 % of the copy bandwidth
+  // against 78 % for the CUDA-core kernel; at head_dim 128 and a few hundred (sequence, head)
+  // pairs its per-block start-up and the coarse waves of two blocks per SM leave the CUDA-core
+  // kernel ahead (75 us against 84 us at the generation shape)
   const bool use_tc = tc_ok && (path == 2 || (path == 0 && D == 64));
   long long n_chunks;
   if (use_tc) {
