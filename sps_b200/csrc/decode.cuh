@@ -195,26 +195,55 @@ __device__ __forceinline__ void merge_slots(const DecodeParams& prm, int sh, int
 // block to arrive merges the records, writes the output and applies the cache update.  Every
 // block takes a ticket, also those past the live length, so that all of them have read the
 // counters before any update.  `wrote` = this block stored a record (its stores are fenced).
+// `local` (tensor-core kernel, one block per (sequence, head)): the block's two records — its
+// tiles and the short segments / current entries — are in shared memory at `local`; there is
+// nobody to take a ticket against, and the merge needs no trip through global memory.
 template <int D, int NQ, bool FP16, bool SLOTS>
 __device__ __forceinline__ void decode_finish(const DecodeParams& prm, int sh, int s, int h, int n_total,
                                               const int (&seg_live)[kMaxSegments], long long ring_len,
                                               long long ring_pos, long long ret_len, bool wrote, int tid,
-                                              int nthreads) {
-  // (the barrier orders the block's record stores before thread 0's fence, which is cumulative)
-  if (wrote) __syncthreads();
-  __shared__ int s_last;
-  if (tid == 0) {
-    if (wrote) __threadfence();
-    const bool last = atomicAdd(&prm.tickets[sh], 1) == (int)gridDim.y - 1;
-    if (last) __threadfence();
-    s_last = last;
+                                              int nthreads, const float* local = nullptr,
+                                              uint32_t local_live = 0) {
+  if (local != nullptr) {
+    __syncthreads();
+    for (int idx = tid; idx < NQ * D; idx += nthreads) {
+      const int qi = idx / D, d = idx % D;
+      float m[2], l[2], a[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float* rec = local + (c * NQ + qi) * (D + 2);
+        const bool live = (local_live >> c) & 1u;
+        m[c] = live ? rec[0] : -1.0e30f;
+        l[c] = live ? rec[1] : 0.f;
+        a[c] = live ? rec[2 + d] : 0.f;
+      }
+      const float mx = fmaxf(m[0], m[1]);
+      const float f0 = fast_exp2(m[0] - mx), f1 = fast_exp2(m[1] - mx);
+      const float lsum = l[0] * f0 + l[1] * f1, asum = a[0] * f0 + a[1] * f1;
+      const float o = lsum > 0.f ? asum / lsum : 0.f;
+      const size_t off = (((size_t)s * NQ + qi) * prm.H + h) * D + d;
+      if (prm.out16)
+        reinterpret_cast<uint16_t*>(prm.out)[off] = (uint16_t)(pack2<FP16>(o, 0.f) & 0xffffu);
+      else
+        reinterpret_cast<float*>(prm.out)[off] = o;
+    }
+  } else {
+    // (the barrier orders the block's record stores before thread 0's fence, which is cumulative)
+    if (wrote) __syncthreads();
+    __shared__ int s_last;
+    if (tid == 0) {
+      if (wrote) __threadfence();
+      const bool last = atomicAdd(&prm.tickets[sh], 1) == (int)gridDim.y - 1;
+      if (last) __threadfence();
+      s_last = last;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    if constexpr (SLOTS)
+      merge_slots<D, NQ, FP16>(prm, sh, s, h, seg_live, tid, nthreads);
+    else
+      merge_records<D, NQ, FP16>(prm, sh, s, h, n_total, tid, nthreads);
   }
-  __syncthreads();
-  if (!s_last) return;
-  if constexpr (SLOTS)
-    merge_slots<D, NQ, FP16>(prm, sh, s, h, seg_live, tid, nthreads);
-  else
-    merge_records<D, NQ, FP16>(prm, sh, s, h, n_total, tid, nthreads);
   const DecodeAppend& ap = prm.app;
   const bool append = ap.br_k != nullptr && ap.active[s] != 0;
   const bool full = ring_len >= ap.window_tokens;
@@ -235,7 +264,7 @@ __device__ __forceinline__ void decode_finish(const DecodeParams& prm, int sh, i
     }
   }
   if (tid == 0) {
-    prm.tickets[sh] = 0;                  // ready for the next launch
+    if (local == nullptr) prm.tickets[sh] = 0;   // ready for the next launch
     if (append && ret_len < ap.retained_storage) ap.br_len[sh] = ret_len + 1;
     if (ap.br_k != nullptr && ap.window_tokens > 0) {
       // the ring counters belong to the sequence: the last of its heads to get here advances them
@@ -273,6 +302,11 @@ __device__ __forceinline__ void cuda_core_chunk(const DecodeParams& prm, int s, 
   const bool worker = tid < kDecodeThreads;
   __shared__ float s_m[4][NQ], s_l[4][NQ], s_acc[4][NQ][D];
   if (worker) {
+    if (with_extras && warp == 0 && lane < 2 * prm.n_extras) {
+      // the single-row entries are read last, by one warp: have them in L2 by then
+      const void* base = (lane & 1) ? prm.extra_v[lane >> 1] : prm.extra_k[lane >> 1];
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint16_t*>(base) + (size_t)sh * D));
+    }
     // queries, pre-scaled so scores are in the log2 domain
     float q[NQ][8];
 #pragma unroll

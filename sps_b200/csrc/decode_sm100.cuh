@@ -32,7 +32,7 @@
 
 namespace spsattn {
 
-constexpr int kTcThreads = 192;      // 4 softmax warps, 1 producer warp, 1 MMA warp
+constexpr int kTcThreads = 320;      // 4 softmax warps, 1 producer warp, 1 MMA warp, 4 CUDA-core warps
 constexpr int kTcTile = 128;         // keys per tile
 constexpr int kTcQPad = 16;          // queries padded to the smallest N of an M = 128 MMA
 constexpr float kTcRescaleLog2 = 8.0f;
@@ -72,7 +72,7 @@ struct DecodeMaps {
 };
 
 template <int D, int NQ, bool FP16>
-__global__ void __launch_bounds__(kTcThreads)
+__global__ void __launch_bounds__(kTcThreads, 2)
 decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm) {
   using Cfg = DecodeTcCfg<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -118,13 +118,18 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
       cc -= prm.seg_chunks[x];
     }
   }
-  float* rec = prm.partial + ((size_t)sh * prm.n_chunks + slot) * NQ * (D + 2);
+  // one block per (sequence, head): its two records stay in shared memory (decode_finish merges
+  // them there); otherwise records go to the workspace and the last block to finish merges
+  const bool solo = gridDim.y == 1;
+  __shared__ __align__(16) float s_rec[2][NQ][D + 2];
+  float* rec = solo ? &s_rec[0][0][0] : prm.partial + ((size_t)sh * prm.n_chunks + slot) * NQ * (D + 2);
+  uint32_t local_live = 0;
   bool wrote = false;
 
   // The current-token entries and the short segments (a ring of a few dozen rows) are not worth
-  // a pipeline of their own: the block of slot 0 runs the CUDA-core routine on them with its
-  // softmax warps — while its first tiles are already in flight — and stores their record in
-  // the last record slot.
+  // a pipeline of their own: the block of slot 0 runs the CUDA-core routine on them with four
+  // warps of its own (6..9), beside the tile pipeline, and stores their record in the last
+  // record slot.
   const bool small_owner = prm.extras_slot >= 0 && slot == 0;
   auto small_work = [&]() {
     int small_start[kMaxSegments + 1];
@@ -132,9 +137,10 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
 #pragma unroll
     for (int x = 0; x < kMaxSegments; ++x)
       small_start[x + 1] = small_start[x] + (((prm.small_segs >> x) & 1u) ? seg_live[x] : 0);
-    float* srec = prm.partial + ((size_t)sh * prm.n_chunks + prm.extras_slot) * NQ * (D + 2);
+    float* srec = solo ? &s_rec[1][0][0]
+                       : prm.partial + ((size_t)sh * prm.n_chunks + prm.extras_slot) * NQ * (D + 2);
     cuda_core_chunk<D, NQ, FP16>(prm, s, h, sh, small_start, 0, small_start[kMaxSegments], prm.n_extras > 0,
-                                 srec, tid);
+                                 srec, tid - 192);
   };
 
   if (seg >= 0 && rows > 0) {
@@ -298,6 +304,9 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
             __syncwarp();
           }
         }
+      } else if (warp >= 6) {
+        // -------------------------------------------------------------- CUDA-core warps
+        if (small_owner) small_work();
       } else {
         // -------------------------------------------------------------- softmax warps
         const int t = tid;                       // key inside the tile = TMEM lane
@@ -310,7 +319,6 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
           l_part[qi] = 0.f;
         }
         bool ok = true;
-        if (small_owner) small_work();
         for (int j = 0; j < n_tiles; ++j) {
           const int sb = j & 1;
           if (!mbar_wait(bar_s_full + 8 * sb, (j >> 1) & 1, abort_flag, prm.status)) {
@@ -469,15 +477,17 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
       tmem_dealloc<Cfg::kTmemCols>(tmem);
     }
     wrote = true;
-    if (bail && small_owner && warp < 4) small_work();
+    if (bail && small_owner && warp >= 6) small_work();
   } else if (small_owner) {
-    if (warp < 4) small_work();
+    if (warp >= 6) small_work();
     wrote = true;
   }
 
   if (prm.tickets == nullptr) return;
+  if (seg >= 0 && rows > 0) local_live |= 1u;
+  if (small_owner) local_live |= 2u;
   decode_finish<D, NQ, FP16, true>(prm, sh, s, h, n_total, seg_live, ring_len, ring_pos, ret_len, wrote, tid,
-                                   kTcThreads);
+                                   kTcThreads, solo ? &s_rec[0][0][0] : nullptr, local_live);
 }
 
 }  // namespace spsattn
