@@ -243,7 +243,8 @@ int spsattn_decode_step(const void* q, int nq, void* out, int out_dtype,
                         int* device_status, void* stream);
 
 /* Test hook: which kernel spsattn_decode_step uses.  0 = automatic (the tensor-core kernel when
- * head_dim is 64 and no segment is packed through seq_offset, else the CUDA-core kernel),
+ * head_dim is 64 or 128, no segment is packed through seq_offset and there are at least 444
+ * (sequence, head, long segment) triples, else the CUDA-core kernel),
  * 1 = always the CUDA-core kernel, 2 = the tensor-core kernel (head_dim 64 or 128, no packed
  * segment) or SPSATTN_ERR_ARG.  Process-wide. */
 int spsattn_debug_decode_path(int path);

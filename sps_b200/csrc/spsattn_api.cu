@@ -194,7 +194,7 @@ int tc_chunk_rows(int S, int H, const spsattn_segment* segs, int n_segments) {
     long long blocks = 0;
     for (int x = 0; x < n_segments; ++x)
       if (segs[x].max_rows > kTcSmallRows) blocks += (segs[x].max_rows + chunk - 1) / chunk;
-    if ((long long)S * H * blocks >= 148LL * 4) break;
+    if ((long long)S * H * blocks >= 148LL * 3) break;
     chunk = (chunk / 2 + kTcTile - 1) / kTcTile * kTcTile;
   }
   return (int)chunk;
@@ -508,11 +508,16 @@ static int decode_impl(const void* q, int nq, void* out, int out_dtype, const sp
   const int path = g_decode_path.load();
   const bool tc_ok = single_launch && tc_supported(segs, n_segments, D);
   if (path == 2 && !tc_ok) return SPSATTN_ERR_ARG;
-  // automatic choice: head_dim 64, where the tensor-core kernel reaches 85 % of the copy bandwidth
-  // against 78 % for the CUDA-core kernel; at head_dim 128 and a few hundred (sequence, head)
-  // pairs its per-block start-up and the coarse waves of two blocks per SM leave the CUDA-core
-  // kernel ahead (75 us against 84 us at the generation shape)
-  const bool use_tc = tc_ok && (path == 2 || (path == 0 && D == 64));
+  // automatic choice: the tensor-core kernel when whole segments, one block each, already fill
+  // the machine (two blocks per SM): then every block streams a long run of tiles, merges in
+  // shared memory and its start-up is amortised (90 % of the copy bandwidth at 128 sequences x 16
+  // heads x 64, 5.1 TB/s against 4.4 at 32 x 16 x 128).  With fewer (sequence, head) pairs the
+  // segments have to be cut into short chunks and the CUDA-core kernel, with its 740 small
+  // resident blocks, is the better fit.
+  long long long_segments = 0;
+  for (int x = 0; x < n_segments; ++x) long_segments += segs[x].max_rows > kTcSmallRows ? 1 : 0;
+  const bool tc_fits = (long long)S * H * long_segments >= 148LL * 3;
+  const bool use_tc = tc_ok && (path == 2 || (path == 0 && tc_fits));
   long long n_chunks;
   if (use_tc) {
     prm.chunk_rows = tc_chunk_rows(S, H, segs, n_segments);
