@@ -38,7 +38,7 @@ GENERATION = "cfg3_xl_generation"
 # DRAM traffic per full-size launch, from ncu captures of a smaller case scaled by the units
 # processed (traffic is proportional to batch rows / sequences)
 PREFILL_DRAM_BYTES_PER_LAUNCH = 2 * (151.4e6 + 33.3e6)
-DECODE_DRAM_BYTES_PER_LAUNCH = 4 * (332.2e6 + 6.2e6)
+DECODE_DRAM_BYTES_PER_LAUNCH = 4 * (332.2e6 + 4.9e6)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 

@@ -162,24 +162,34 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
 
     if (tid == 0)
       s_abort = (prm.status != nullptr && *reinterpret_cast<volatile int*>(prm.status) != 0) ? 1 : 0;
-    // zero P and the padded query tile, then place the nq query rows (K-major, 128-byte swizzle:
-    // 16-byte chunk ch of row r of a 64-wide sub-tile sits at r * 128 + ((ch ^ (r & 7)) << 4))
-    {
-      uint8_t* gen = smem_raw + (smem_base - smem_u32(smem_raw));
-      uint4* zp = reinterpret_cast<uint4*>(gen + Cfg::kOffP);
-      for (int i = tid; i < Cfg::kPBytes / 16; i += kTcThreads) zp[i] = make_uint4(0, 0, 0, 0);
-      uint4* zq = reinterpret_cast<uint4*>(gen + Cfg::kOffQ);
-      for (int i = tid; i < Cfg::kQBytes / 16; i += kTcThreads) zq[i] = make_uint4(0, 0, 0, 0);
-      __syncthreads();
-      if (tid < NQ * (D / 8)) {
-        const int r = tid / (D / 8), chunk = tid % (D / 8);
-        const int c = chunk / 8, ch = chunk % 8;
-        const uint4 u = *reinterpret_cast<const uint4*>(
-            reinterpret_cast<const uint16_t*>(prm.q) + (((size_t)s * NQ + r) * prm.H + h) * D + chunk * 8);
-        *reinterpret_cast<uint4*>(gen + Cfg::kOffQ + c * Cfg::kQSub + r * 128 + ((ch ^ (r & 7)) << 4)) = u;
-      }
-      fence_proxy_async_smem();
+    // The nq query rows go into the padded query tile (K-major, 128-byte swizzle: 16-byte chunk ch
+    // of row r of a 64-wide sub-tile sits at r * 128 + ((ch ^ (r & 7)) << 4)).  Its other rows,
+    // and rows >= nq of P, are left as they are: they only produce score columns and accumulator
+    // rows that nobody reads, and an MMA row never mixes with another.
+    uint8_t* gen0 = smem_raw + (smem_base - smem_u32(smem_raw));
+    if (tid < NQ * (D / 8)) {
+      const int r = tid / (D / 8), chunk = tid % (D / 8);
+      const int c = chunk / 8, ch = chunk % 8;
+      const uint4 u = *reinterpret_cast<const uint4*>(
+          reinterpret_cast<const uint16_t*>(prm.q) + (((size_t)s * NQ + r) * prm.H + h) * D + chunk * 8);
+      *reinterpret_cast<uint4*>(gen0 + Cfg::kOffQ + c * Cfg::kQSub + r * 128 + ((ch ^ (r & 7)) << 4)) = u;
     }
+    fence_proxy_async_smem();
+    const int n_units = n_tiles * Cfg::kUnitsPerTile;
+    // unit g of the stream: tile g / kUnitsPerTile; first the K units of the tile, then its V units
+    auto issue_unit = [&](int g) {
+      const int slot = g % Cfg::kRing;
+      const int j = g / Cfg::kUnitsPerTile, w = g % Cfg::kUnitsPerTile;
+      const bool is_v = w >= Cfg::kUnitsPerOperand;
+      const int c = w % Cfg::kUnitsPerOperand;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(bar_full + 8 * slot, Cfg::kUnit);
+        tma_load_4d(sRing + slot * Cfg::kUnit, is_v ? &maps.v[seg] : &maps.k[seg], bar_full + 8 * slot,
+                    c * 64, row0 + j * kTcTile, h, s);
+      }
+      __syncwarp();
+    };
+    const int n_early = min(Cfg::kRing, n_units);
     if (warp == 4) {
       if (lane == 0) {
         for (int x = 0; x < Cfg::kRing; ++x) {
@@ -200,6 +210,10 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
         tma_prefetch_desc(&maps.v[seg]);
       }
       __syncwarp();
+      // the first ring of units is requested before the rest of the block is ready: their round
+      // trip to memory overlaps the tensor-memory allocation and the block barrier
+      for (int g = 0; g < n_early; ++g) issue_unit(g);
+    } else if (warp == 5) {
       tmem_alloc<Cfg::kTmemCols>(smem_u32(&s_tmem_base));
       tmem_relinquish();
     }
@@ -213,22 +227,10 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
     if (!bail) {
       if (warp == 4) {
         // -------------------------------------------------------------- TMA producer
-        // unit g of the stream: tile g / kUnitsPerTile; first the K units of the tile, then its V units
-        const int n_units = n_tiles * Cfg::kUnitsPerTile;
-        for (int g = 0; g < n_units; ++g) {
+        for (int g = n_early; g < n_units; ++g) {
           const int slot = g % Cfg::kRing;
-          if (g >= Cfg::kRing &&
-              !warp_wait(bar_empty + 8 * slot, ((g / Cfg::kRing) - 1) & 1, abort_flag, prm.status))
-            break;
-          const int j = g / Cfg::kUnitsPerTile, w = g % Cfg::kUnitsPerTile;
-          const bool is_v = w >= Cfg::kUnitsPerOperand;
-          const int c = w % Cfg::kUnitsPerOperand;
-          if (elect_one()) {
-            mbar_arrive_expect_tx(bar_full + 8 * slot, Cfg::kUnit);
-            tma_load_4d(sRing + slot * Cfg::kUnit, is_v ? &maps.v[seg] : &maps.k[seg], bar_full + 8 * slot,
-                        c * 64, row0 + j * kTcTile, h, s);
-          }
-          __syncwarp();
+          if (!warp_wait(bar_empty + 8 * slot, ((g / Cfg::kRing) - 1) & 1, abort_flag, prm.status)) break;
+          issue_unit(g);
         }
       } else if (warp == 5) {
         // -------------------------------------------------------------- MMA issuer
@@ -469,10 +471,15 @@ decode_tc_kernel(const __grid_constant__ DecodeMaps maps, const DecodeParams prm
         }
       }
     }
+    if (bail && warp == 4) {
+      // nothing will consume the units requested early: let them land before the block goes
+      for (int g = 0; g < n_early; ++g)
+        if (!warp_wait(bar_full + 8 * (g % Cfg::kRing), 0, abort_flag, nullptr)) break;
+    }
     // common teardown: every role arrives here, also after a failed wait
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 5) {
       tc_fence_after();
       tmem_dealloc<Cfg::kTmemCols>(tmem);
     }
