@@ -54,7 +54,8 @@ class Dims:
 
 
 # (prediction slot, persistent-key parity) per model family
-VARIANTS = {"sps": (1, sps_oracle.PARITY_EVEN), "reverse_sps": (0, sps_oracle.PARITY_ODD)}
+VARIANTS = {"sps": (1, sps_oracle.PARITY_EVEN), "reverse_sps": (0, sps_oracle.PARITY_ODD),
+            "delayed_state": (1, sps_oracle.PARITY_ODD)}   # delayed_state/inference.py:8-10, core.py:49
 
 
 def document_idx(idx: torch.Tensor, eos: int, pad: int) -> torch.Tensor:

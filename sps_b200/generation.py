@@ -39,6 +39,8 @@ _VARIANTS = {
     # name: (prediction slot, ring ("window") slot, retained slot, persistent-key parity)
     "sps": (1, 1, 0, _lib.PARITY_EVEN),            # sps/inference.py:8-12
     "reverse_sps": (0, 0, 1, _lib.PARITY_ODD),     # reverse_sps/inference.py:58-62
+    "delayed_state": (1, 0, 1, _lib.PARITY_ODD),   # delayed_state/inference.py:8-10: Reverse-SPS caches and
+                                                   # attention, logits read at the odd slot
 }
 
 
@@ -597,7 +599,11 @@ def generator_for(model, *, param_dtype: Optional[torch.dtype] = None) -> SPSGen
                    intermediate_size=int(cfg.intermediate_size), norm_eps=float(cfg.norm_eps),
                    eos_token_id=int(cfg.eos_token_id), pad_token_id=int(cfg.pad_token_id),
                    predict_token_id=int(cfg.predict_token_id), window_size=int(cfg.window_size))
-    variant = "sps" if int(getattr(model, "_prediction_slot_index", 0)) == 1 else "reverse_sps"
+    slots = (int(getattr(model, "_prediction_slot_index", 0)), int(getattr(model, "_window_slot_index", 0)),
+             int(getattr(model, "_retained_slot_index", 1)))
+    variant = next((name for name, v in _VARIANTS.items() if v[:3] == slots), None)
+    if variant is None:
+        raise ValueError(f"unknown slot assignment {slots}")
     sd = model.state_dict()
     first = next(iter(sd.values()))
     if param_dtype is None:

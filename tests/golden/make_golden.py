@@ -290,6 +290,7 @@ def model_cases():
     import types
     import modeling.models.sps.core as sps_core
     import modeling.models.reverse_sps.core as rsps_core
+    from modeling.models.delayed_state import DelayedStateConfig, DelayedStateModel
     from modeling.models.reverse_sps import ReverseSPSConfig, ReverseSPSModel
     from modeling.models.reverse_sps.inference import ReverseSPSInferenceMixin as Mixin
     from modeling.models.sps import SPSConfig, SPSModel
@@ -312,7 +313,8 @@ def model_cases():
     sps_core.triton_sps_sliding_attention = sps_attn
     rsps_core.triton_reverse_sps_sliding_attention = rsps_attn
     for tag, cfg_cls, model_cls, w in (("sps", SPSConfig, SPSModel, 2), ("sps_w5", SPSConfig, SPSModel, 5),
-                                       ("rsps", ReverseSPSConfig, ReverseSPSModel, 3)):
+                                       ("rsps", ReverseSPSConfig, ReverseSPSModel, 3),
+                                       ("ds", DelayedStateConfig, DelayedStateModel, 3)):
         torch.manual_seed(41)
         cfg = cfg_cls(block_size=32, vocab_size=64, n_layer=2, n_head=2, hidden_size=128,
                       intermediate_size=256, dropout=0.0, bias=False, eos_token_id=63, pad_token_id=62,
@@ -336,7 +338,7 @@ def model_cases():
         eos, pad = cfg.eos_token_id, cfg.pad_token_id
         g = torch.Generator().manual_seed(43)
         dense_idx = torch.randint(0, 60, (2, 12), generator=g)
-        if tag != "rsps":
+        if tag not in ("rsps", "ds"):
             dense_idx[1, 4] = eos
         put(f"model_{tag}_dense_idx", dense_idx)
         put(f"model_{tag}_dense_logits", model(dense_idx))

@@ -9,7 +9,7 @@ from oracle import sps_model_oracle as mo
 from tests.golden.loader import load_golden
 
 G = load_golden()
-TAGS = {"sps": "sps", "sps_w5": "sps", "rsps": "reverse_sps"}
+TAGS = {"sps": "sps", "sps_w5": "sps", "rsps": "reverse_sps", "ds": "delayed_state"}
 
 
 def golden_model(tag):
