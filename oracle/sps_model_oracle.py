@@ -55,7 +55,10 @@ class Dims:
 
 # (prediction slot, persistent-key parity) per model family
 VARIANTS = {"sps": (1, sps_oracle.PARITY_EVEN), "reverse_sps": (0, sps_oracle.PARITY_ODD),
-            "delayed_state": (1, sps_oracle.PARITY_ODD)}   # delayed_state/inference.py:8-10, core.py:49
+            "delayed_state": (1, sps_oracle.PARITY_ODD),   # delayed_state/inference.py:8-10, core.py:49
+            # Standard model: no <predict> rows, causal attention inside a document
+            # (full_attention_model.py:77-122, :744-853)
+            "standard": (0, sps_oracle.PARITY_NONE)}
 
 
 def document_idx(idx: torch.Tensor, eos: int, pad: int) -> torch.Tensor:
@@ -110,24 +113,27 @@ def hidden_states(weights: Dict[str, torch.Tensor], dims: Dims, idx: torch.Tenso
     b, t = idx.shape
     nh, c = dims.n_head, dims.hidden_size
     hd = c // nh
-    docs2 = document_idx(idx, dims.eos_token_id, dims.pad_token_id).repeat_interleave(2, dim=1)
+    rep = 1 if variant == "standard" else 2     # rows per token
+    docs2 = document_idx(idx, dims.eos_token_id, dims.pad_token_id).repeat_interleave(rep, dim=1)
     pos = torch.arange(t).unsqueeze(0).expand(b, -1) if positions is None else positions
-    fc = freqs_cis(hd, dims.block_size)[pos.repeat_interleave(2, dim=1)]      # [B, 2T, hd/2]
-    idx2 = idx.repeat_interleave(2, dim=1)
-    idx2[:, 1::2] = dims.predict_token_id
+    fc = freqs_cis(hd, dims.block_size)[pos.repeat_interleave(rep, dim=1)]     # [B, rep*T, hd/2]
+    idx2 = idx.repeat_interleave(rep, dim=1)
+    if rep == 2:
+        idx2[:, 1::2] = dims.predict_token_id
+    n_rows = idx2.shape[1]
     x = w["transformer.wte.weight"][idx2]
     for layer in range(dims.n_layer):
         pre = f"transformer.h.{layer}."
         xn = _rmsnorm(x, w[pre + "attention_norm.weight"], dims.norm_eps)
         q, k, v = (xn @ w[pre + "attn.c_attn.weight"].T).split(c, dim=2)
-        q = _rope(q.view(b, 2 * t, nh, hd), fc).to(operand_dtype).float().transpose(1, 2)
-        k = _rope(k.view(b, 2 * t, nh, hd), fc).to(operand_dtype).float().transpose(1, 2)
-        v = v.view(b, 2 * t, nh, hd).to(operand_dtype).float().transpose(1, 2)
+        q = _rope(q.view(b, n_rows, nh, hd), fc).to(operand_dtype).float().transpose(1, 2)
+        k = _rope(k.view(b, n_rows, nh, hd), fc).to(operand_dtype).float().transpose(1, 2)
+        v = v.view(b, n_rows, nh, hd).to(operand_dtype).float().transpose(1, 2)
         y = sps_oracle.prefill_attention(q, k, v, 1.0 / math.sqrt(hd), persistent_parity=parity,
                                          temporary_window=dims.window_size, docs=docs2)
         if round_output:
             y = y.to(operand_dtype).float()
-        y = y.transpose(1, 2).reshape(b, 2 * t, c)
+        y = y.transpose(1, 2).reshape(b, n_rows, c)
         x = x + y @ w[pre + "attn.c_proj.weight"].T
         xn = _rmsnorm(x, w[pre + "mlp_norm.weight"], dims.norm_eps)
         gate = torch.nn.functional.silu(xn @ w[pre + "mlp.gate_proj.weight"].T)
@@ -142,7 +148,8 @@ def logits(weights, dims: Dims, idx: torch.Tensor, *, variant: str = "sps",
     slot, _ = VARIANTS[variant]
     x = hidden_states(weights, dims, idx, variant=variant, positions=positions,
                       operand_dtype=operand_dtype, round_output=round_output)
-    return x[:, slot::2] @ weights["lm_head.weight"].float().T
+    rep = 1 if variant == "standard" else 2
+    return x[:, slot::rep] @ weights["lm_head.weight"].float().T
 
 
 def greedy_token(logits_BxV: torch.Tensor, dims: Dims,
@@ -150,7 +157,8 @@ def greedy_token(logits_BxV: torch.Tensor, dims: Dims,
     """utils/sampling.py:55-83 with do_sample=False: argmax with <predict>, pad and the caller's
     forbidden ids suppressed (reverse_sps/inference.py:893-902)."""
     z = logits_BxV.float().clone()
-    z[:, dims.predict_token_id] = float("-inf")
+    if dims.predict_token_id is not None and dims.predict_token_id >= 0:
+        z[:, dims.predict_token_id] = float("-inf")
     z[:, dims.pad_token_id] = float("-inf")
     if forbidden is not None and len(forbidden):
         z[:, torch.as_tensor(list(forbidden), dtype=torch.long)] = float("-inf")
@@ -179,7 +187,8 @@ def generate(weights, dims: Dims, idx: torch.Tensor, max_new_tokens: int, *, var
         z = lg[torch.arange(b), last_real]
         tok = greedy_token(z, dims, forbidden)
         zz = z.float().clone()
-        zz[:, dims.predict_token_id] = float("-inf")
+        if dims.predict_token_id is not None and dims.predict_token_id >= 0:
+            zz[:, dims.predict_token_id] = float("-inf")
         zz[:, dims.pad_token_id] = float("-inf")
         if forbidden is not None and len(forbidden):
             zz[:, torch.as_tensor(list(forbidden), dtype=torch.long)] = float("-inf")

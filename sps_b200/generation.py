@@ -1,4 +1,5 @@
-"""Greedy generation for the SPS model family with the attention path of this library.
+"""Greedy generation for the SPS model family (SPS, Reverse-SPS, Delayed-State) and the Standard
+model with the attention path of this library.
 
 ``SPSGenerator`` runs the reference's decoder (RMSNorm, fused q/k/v projection, rotary embedding,
 SPS attention, output projection, SwiGLU MLP, tied head) from a state dict with the reference's
@@ -13,6 +14,8 @@ synchronisation, allocation or Python between tokens.  Reference behaviour being
                greedy sampling, <predict> and pad suppressed (utils/sampling.py:55-83,
                reverse_sps/inference.py:893-902)
   * the model  src/modeling/models/model.py:101-132, :201-230, :304-327; sps/core.py:35-82, :100-131
+  * Standard   src/modeling/models/full_attention_model.py:506-740 (one row per token, the cache holds
+               the current document, one query per step)
 
 What runs where: the projections and the head are library GEMMs (``torch.mm``); everything else
 on the per-token chain is a kernel of libspsattn.so — residual add + RMSNorm, rotary + cast of
@@ -41,6 +44,9 @@ _VARIANTS = {
     "reverse_sps": (0, 0, 1, _lib.PARITY_ODD),     # reverse_sps/inference.py:58-62
     "delayed_state": (1, 0, 1, _lib.PARITY_ODD),   # delayed_state/inference.py:8-10: Reverse-SPS caches and
                                                    # attention, logits read at the odd slot
+    # Standard model (full_attention_model.py): one row per token, no <predict> slot and no ring;
+    # the cache holds the current document (:506-585), causal attention inside a document
+    "standard": (0, None, 0, _lib.PARITY_NONE),
 }
 
 
@@ -177,6 +183,8 @@ class SPSGenerator:
         self.dims = dims
         self.variant = variant
         self.pred_slot, self.window_slot, self.retained_slot, self.parity = _VARIANTS[variant]
+        self.n_slot = 1 if variant == "standard" else 2          # rows per token
+        self.window_tokens = 0 if variant == "standard" else int(dims.window_size)
         self.device = torch.device(device)
         self.param_dtype = param_dtype
         self.attn_dtype = torch.bfloat16                       # reverse_sps/inference.py:637
@@ -219,13 +227,15 @@ class SPSGenerator:
         """Final-norm hidden states [B, 2T, C] of the doubled prompt; fills ``state`` on the way."""
         d = self.dims
         b, t = idx.shape
-        n, c, h, hd, inter = 2 * t, d.hidden_size, d.n_head, d.head_dim, d.intermediate_size
+        ns = self.n_slot
+        n, c, h, hd, inter = ns * t, d.hidden_size, d.n_head, d.head_dim, d.intermediate_size
         rows = b * n
         dev, pdt = self.device, self.param_dtype
-        idx2 = idx.repeat_interleave(2, dim=1)
-        idx2[:, 1::2] = d.predict_token_id                                  # reverse_sps/core.py:261-264
+        idx2 = idx.repeat_interleave(ns, dim=1)
+        if ns == 2:
+            idx2[:, 1::2] = d.predict_token_id                              # reverse_sps/core.py:261-264
         x = self.w.wte.index_select(0, idx2.reshape(-1))                    # [rows, C] residual stream
-        fc = self.freqs[positions.repeat_interleave(2, dim=1)].contiguous()  # [B, 2T, hd/2, 2]
+        fc = self.freqs[positions.repeat_interleave(ns, dim=1)].contiguous()  # [B, N, hd/2, 2]
         xn = torch.empty_like(x)
         delta = torch.empty_like(x)
         qkv = torch.empty((rows, 3 * c), device=dev, dtype=pdt)
@@ -250,7 +260,7 @@ class SPSGenerator:
                 self._fill_caches(state, layer, ops[1], ops[2], doc_mask)
             in_place = hd in (64, 128)     # the tensor-core kernel reads and writes token-major rows
             o = prefill_attention(ops[0].transpose(1, 2), ops[1].transpose(1, 2), ops[2].transpose(1, 2),
-                                  scale, persistent_parity=self.parity, temporary_window=d.window_size,
+                                  scale, persistent_parity=self.parity, temporary_window=self.window_tokens,
                                   documents_idx=docs2, out=y.transpose(1, 2) if in_place else None)
             if not in_place:
                 y.copy_(o.transpose(1, 2))
@@ -265,24 +275,26 @@ class SPSGenerator:
         return xn.view(b, n, c)
 
     def _fill_caches(self, st: DecodeState, layer: int, k: Tensor, v: Tensor, doc_mask: Tensor) -> None:
-        d = self.dims
         b, n, h, hd = k.shape
         ring = [None] * 4
-        if d.window_size > 0:
+        if self.window_tokens > 0:
             ring = [st.nw_k[layer].data_ptr(), st.nw_v[layer].data_ptr(), st.nw_len[layer].data_ptr(),
                     st.nw_pos[layer].data_ptr()]
+        # the entry point addresses row 2 * token + slot of a doubled sequence; with one row per
+        # token (Standard) half the row stride and slot 0 address row `token`
+        row_stride = k.stride(1) if self.n_slot == 2 else k.stride(1) // 2
         rc = self.lib.spsattn_fill_decode_caches(
-            k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1), k.stride(2), doc_mask.data_ptr(),
+            k.data_ptr(), v.data_ptr(), k.stride(0), row_stride, k.stride(2), doc_mask.data_ptr(),
             st.br_k[layer].data_ptr(), st.br_v[layer].data_ptr(), st.br_len[layer].data_ptr(),
-            ring[0], ring[1], ring[2], ring[3], b, n // 2, h, hd, st.max_tokens, int(st.nw_k.shape[3]),
-            int(d.window_size), self.retained_slot, self.window_slot, self._stream())
+            ring[0], ring[1], ring[2], ring[3], b, n // self.n_slot, h, hd, st.max_tokens, int(st.nw_k.shape[3]),
+            self.window_tokens, self.retained_slot, self.window_slot or 0, self._stream())
         _lib.check(rc, "spsattn_fill_decode_caches")
 
     def build_decode_state(self, batch_size: int, max_tokens: int) -> DecodeState:
         """reverse_sps/inference.py:64-111, one allocation per kind instead of one per layer."""
         d = self.dims
         dev, L, h, hd = self.device, d.n_layer, d.n_head, d.head_dim
-        storage = max(int(d.window_size), 1)
+        storage = max(self.window_tokens, 1)
         z = lambda *s, dt: torch.zeros(s, device=dev, dtype=dt)
         return DecodeState(
             nw_k=z(L, batch_size, h, storage, hd, dt=self.attn_dtype),
@@ -302,12 +314,12 @@ class SPSGenerator:
         idx = idx_BxT.to(self.device)
         b, t = idx.shape
         if t > self.dims.block_size:
-            raise ValueError(f"Cannot forward sequence of length {2 * t}, block size is only {self.dims.block_size}")
+            raise ValueError(f"Cannot forward sequence of length {self.n_slot * t}, block size is only {self.dims.block_size}")
         docs2 = left_padded_document_idx(idx, self.dims.eos_token_id, self.dims.pad_token_id)
-        docs2 = docs2.repeat_interleave(2, dim=1).contiguous()
+        docs2 = docs2.repeat_interleave(self.n_slot, dim=1).contiguous()
         pos = torch.arange(t, device=self.device).unsqueeze(0).expand(b, -1)
         xn = self._prefill_chain(idx, pos, docs2, None, None)
-        pred = xn[:, self.pred_slot::2].reshape(b * t, -1)
+        pred = xn[:, self.pred_slot::self.n_slot].reshape(b * t, -1)
         return torch.mm(pred, self.w.lm_head.t()).view(b, t, -1)
 
     @torch.no_grad()
@@ -331,11 +343,16 @@ class SPSGenerator:
         else:
             state = self.build_decode_state(b, total)
         docs = left_padded_document_idx(idx, d.eos_token_id, d.pad_token_id)
-        docs2 = docs.repeat_interleave(2, dim=1).contiguous()
-        doc_mask = (real & (docs == docs[:, -1:])).to(torch.uint8).contiguous()
+        docs2 = docs.repeat_interleave(self.n_slot, dim=1).contiguous()
+        doc_mask = real & (docs == docs[:, -1:])
+        if self.variant == "standard":
+            # a prompt that ends on EOS starts decoding with an empty cache
+            # (full_attention_model.py:703-705)
+            doc_mask = doc_mask & (idx[:, -1:] != d.eos_token_id)
+        doc_mask = doc_mask.to(torch.uint8).contiguous()
         pos = left_padded_position_ids(idx, d.pad_token_id)
         xn = self._prefill_chain(idx, pos, docs2, state, doc_mask)
-        last = xn[:, 2 * (t - 1) + self.pred_slot]                          # [B, C]
+        last = xn[:, self.n_slot * (t - 1) + self.pred_slot]                # [B, C]
         next_logits = torch.mm(last, self.w.lm_head.t())
         state.processed_tokens.copy_(real_lengths)
         state.next_doc_start.copy_(idx[:, -1] == d.eos_token_id)
@@ -354,29 +371,30 @@ class SPSGenerator:
         s.token = torch.zeros(b, device=dev, dtype=torch.long)
         s.active = torch.zeros(b, device=dev, dtype=torch.bool)
         s.active_i8 = torch.zeros(b, device=dev, dtype=torch.int8)
-        s.idx_pair = torch.full((b, 2), d.predict_token_id, device=dev, dtype=torch.long)
+        ns, wt = self.n_slot, self.window_tokens
+        s.idx_pair = torch.full((b, ns), max(d.predict_token_id, 0), device=dev, dtype=torch.long)
         s.pos = torch.zeros(b, device=dev, dtype=torch.long)
         s.fc = torch.zeros((b, hd // 2, 2), device=dev, dtype=torch.float32)
-        s.x = torch.zeros((2 * b, c), device=dev, dtype=pdt)
+        s.x = torch.zeros((ns * b, c), device=dev, dtype=pdt)
         s.xn = torch.zeros_like(s.x)
         s.delta = torch.zeros_like(s.x)
-        s.qkv = torch.zeros((2 * b, 3 * c), device=dev, dtype=pdt)
-        s.q = torch.zeros((b, 2, h, hd), device=dev, dtype=self.attn_dtype)
-        s.k2 = torch.zeros((2, b, h, hd), device=dev, dtype=self.attn_dtype)
-        s.v2 = torch.zeros((2, b, h, hd), device=dev, dtype=self.attn_dtype)
-        s.y = torch.zeros((2 * b, c), device=dev, dtype=self.attn_dtype)
-        s.y_param = s.y if pdt == self.attn_dtype else torch.zeros((2 * b, c), device=dev, dtype=pdt)
-        s.gate_up = torch.zeros((2 * b, 2 * inter), device=dev, dtype=pdt)
-        s.hidden = torch.zeros((2 * b, inter), device=dev, dtype=pdt)
+        s.qkv = torch.zeros((ns * b, 3 * c), device=dev, dtype=pdt)
+        s.q = torch.zeros((b, ns, h, hd), device=dev, dtype=self.attn_dtype)
+        s.k2 = torch.zeros((ns, b, h, hd), device=dev, dtype=self.attn_dtype)
+        s.v2 = torch.zeros((ns, b, h, hd), device=dev, dtype=self.attn_dtype)
+        s.y = torch.zeros((ns * b, c), device=dev, dtype=self.attn_dtype)
+        s.y_param = s.y if pdt == self.attn_dtype else torch.zeros((ns * b, c), device=dev, dtype=pdt)
+        s.gate_up = torch.zeros((ns * b, 2 * inter), device=dev, dtype=pdt)
+        s.hidden = torch.zeros((ns * b, inter), device=dev, dtype=pdt)
         s.logits = torch.zeros((b, d.vocab_size), device=dev, dtype=pdt)
         s.zero_tok = torch.zeros(b, device=dev, dtype=torch.long)
-        # the [B, 2, 3C] projection seen as one row per sequence with 6 head groups:
-        # slot 0 q, k, v, slot 1 q, k, v
-        groups = (_lib.RopeGroup * 6)()
+        # the [B, ns, 3C] projection seen as one row per sequence with 3 * ns head groups:
+        # slot 0 q, k, v (, slot 1 q, k, v)
+        groups = (_lib.RopeGroup * (3 * ns))()
         hs = h * hd
-        for slot in range(2):
+        for slot in range(ns):
             gq, gk, gv = groups[3 * slot], groups[3 * slot + 1], groups[3 * slot + 2]
-            gq.out, gq.stride_b, gq.rotate = s.q.data_ptr() + slot * hs * 2, 2 * hs, 1
+            gq.out, gq.stride_b, gq.rotate = s.q.data_ptr() + slot * hs * 2, ns * hs, 1
             gk.out, gk.stride_b, gk.rotate = s.k2[slot].data_ptr(), hs, 1
             gv.out, gv.stride_b, gv.rotate = s.v2[slot].data_ptr(), hs, 0
             for g in (gq, gk, gv):
@@ -388,38 +406,42 @@ class SPSGenerator:
         for layer in range(L):
             segs = (_lib.Segment * 2)()
             n_seg = 0
-            if d.window_size > 0:                                          # reverse_sps/inference.py:333-342
+            qm_all = (1 << ns) - 1
+            if wt > 0:                                                     # reverse_sps/inference.py:333-342
                 sg = segs[n_seg]
                 sg.k, sg.v = state.nw_k[layer].data_ptr(), state.nw_v[layer].data_ptr()
                 sg.seq_offset, sg.seq_stride = None, h * storage * hd
                 sg.head_stride, sg.row_stride = storage * hd, hd
                 sg.lengths, sg.lengths_per_head = state.nw_len[layer].data_ptr(), 0
-                sg.max_rows, sg.query_mask = max(1, min(int(d.window_size), state.max_tokens)), 3
+                sg.max_rows, sg.query_mask = max(1, min(wt, state.max_tokens)), qm_all
                 n_seg += 1
             sg = segs[n_seg]                                               # :343-350
             sg.k, sg.v = state.br_k[layer].data_ptr(), state.br_v[layer].data_ptr()
             sg.seq_offset, sg.seq_stride = None, h * state.max_tokens * hd
             sg.head_stride, sg.row_stride = state.max_tokens * hd, hd
             sg.lengths, sg.lengths_per_head = state.br_len[layer].data_ptr(), 1
-            sg.max_rows, sg.query_mask = state.max_tokens, 3
+            sg.max_rows, sg.query_mask = state.max_tokens, qm_all
             n_seg += 1
-            extras = (_lib.Extra * 2)()                                     # decode_attention.py:354-361
-            extras[0].k, extras[0].v, extras[0].query_mask = s.k2[0].data_ptr(), s.v2[0].data_ptr(), 3
-            extras[1].k, extras[1].v, extras[1].query_mask = s.k2[1].data_ptr(), s.v2[1].data_ptr(), 2
+            # the row(s) of this step: every slot sees the input row, only the <predict> slot its own
+            # (decode_attention.py:354-361); Standard: the one row (full_attention_model.py:549-563)
+            extras = (_lib.Extra * 2)()
+            extras[0].k, extras[0].v, extras[0].query_mask = s.k2[0].data_ptr(), s.v2[0].data_ptr(), qm_all
+            if ns == 2:
+                extras[1].k, extras[1].v, extras[1].query_mask = s.k2[1].data_ptr(), s.v2[1].data_ptr(), 2
             ap = _lib.KvAppend()
-            if d.window_size > 0:
+            if wt > 0:
                 ap.nw_k, ap.nw_v = state.nw_k[layer].data_ptr(), state.nw_v[layer].data_ptr()
                 ap.nw_len, ap.nw_pos = state.nw_len[layer].data_ptr(), state.nw_pos[layer].data_ptr()
+                ap.k_window, ap.v_window = s.k2[self.window_slot].data_ptr(), s.v2[self.window_slot].data_ptr()
             ap.br_k, ap.br_v = state.br_k[layer].data_ptr(), state.br_v[layer].data_ptr()
             ap.br_len = state.br_len[layer].data_ptr()
-            ap.k_window, ap.v_window = s.k2[self.window_slot].data_ptr(), s.v2[self.window_slot].data_ptr()
             ap.k_retained, ap.v_retained = (s.k2[self.retained_slot].data_ptr(),
                                             s.v2[self.retained_slot].data_ptr())
             ap.active = s.active_i8.data_ptr()
             ap.window_storage, ap.retained_storage = storage, state.max_tokens
-            ap.window_tokens = int(d.window_size)
+            ap.window_tokens = wt
             s.layer_args.append((segs, n_seg, extras, ap))
-            ws_bytes = max(ws_bytes, self.lib.spsattn_decode_step_workspace_bytes(b, h, hd, 2, segs, n_seg))
+            ws_bytes = max(ws_bytes, self.lib.spsattn_decode_step_workspace_bytes(b, h, hd, ns, segs, n_seg))
         s.ws = torch.zeros(ws_bytes, device=dev, dtype=torch.uint8)
         s.ws_bytes = ws_bytes
         self._step = s
@@ -428,7 +450,7 @@ class SPSGenerator:
         """One token for every row: reads ``token`` / ``active`` of the bound buffers, leaves the
         prediction logits in ``logits`` and the caches and counters advanced.  No host sync."""
         s, d, st = self._step, self.dims, self._step.state
-        b, c, h, hd = s.b, d.hidden_size, d.n_head, d.head_dim
+        b, c, h, hd, ns = s.b, d.hidden_size, d.n_head, d.head_dim, self.n_slot
         stream = self._stream()
         torch.where(s.active, s.token, s.zero_tok, out=s.idx_pair[:, 0])     # inference.py:391-398
         torch.where(s.active, st.processed_tokens, s.zero_tok, out=s.pos)    # :399-403
@@ -445,12 +467,12 @@ class SPSGenerator:
         for layer in range(d.n_layer):
             segs, n_seg, extras, ap = s.layer_args[layer]
             torch.mm(s.xn, self.w.c_attn[layer].t(), out=s.qkv)
-            rc = self.lib.spsattn_qkv_rope_cast(s.qkv.data_ptr(), self.x_dtype_code, 6 * c, 0, hd,
-                                                s.fc.data_ptr(), hd // 2, s.groups, 6, _lib.DTYPE_BF16,
+            rc = self.lib.spsattn_qkv_rope_cast(s.qkv.data_ptr(), self.x_dtype_code, 3 * ns * c, 0, hd,
+                                                s.fc.data_ptr(), hd // 2, s.groups, 3 * ns, _lib.DTYPE_BF16,
                                                 b, 1, h, hd, stream)
             _lib.check(rc, "spsattn_qkv_rope_cast")
-            rc = self.lib.spsattn_decode_step(s.q.data_ptr(), 2, s.y.data_ptr(), _lib.DTYPE_BF16, segs, n_seg,
-                                              extras, 2, C.byref(ap), b, h, hd, _lib.DTYPE_BF16, scale,
+            rc = self.lib.spsattn_decode_step(s.q.data_ptr(), ns, s.y.data_ptr(), _lib.DTYPE_BF16, segs, n_seg,
+                                              extras, ns, C.byref(ap), b, h, hd, _lib.DTYPE_BF16, scale,
                                               s.ws.data_ptr(), s.ws_bytes, _status(self.device).data_ptr(),
                                               stream)
             _lib.check(rc, "spsattn_decode_step")
@@ -461,7 +483,7 @@ class SPSGenerator:
             self._mlp(layer, s.xn, s.gate_up, s.hidden, s.delta)
             nxt = self.w.attn_norm[layer + 1] if layer + 1 < d.n_layer else self.w.out_norm
             self._add_rmsnorm(s.x, s.delta, nxt, s.xn)
-        pred = s.xn.view(b, 2, c)[:, self.pred_slot]
+        pred = s.xn.view(b, ns, c)[:, self.pred_slot]
         torch.mm(pred, self.w.lm_head.t(), out=s.logits)
         # _advance_decode_state (:487-503)
         st.processed_tokens.add_(s.active.to(torch.long))
@@ -499,7 +521,8 @@ class SPSGenerator:
         if max_new_tokens == 0:
             return idx.clone()
         b = idx.shape[0]
-        sup = [d.predict_token_id, d.pad_token_id]                          # inference.py:893-902
+        # inference.py:893-902; the Standard model suppresses pad only (full_attention_model.py:494-499)
+        sup = [d.pad_token_id] + ([d.predict_token_id] if self.n_slot == 2 else [])
         if forbidden_token_ids is not None:
             sup += [int(x) for x in forbidden_token_ids.reshape(-1).tolist()]
         sup = tuple(sorted(set(sup)))
@@ -594,16 +617,21 @@ def generator_for(model, *, param_dtype: Optional[torch.dtype] = None) -> SPSGen
     DelayedStateModel: its ``config`` supplies the dimensions, its ``state_dict()`` the parameters,
     its slot indices (sps/inference.py:8-12, reverse_sps/inference.py:58-62) the variant."""
     cfg = model.config
+    is_standard = not hasattr(cfg, "predict_token_id")      # full_attention_model.ModelConfig
     dims = SPSDims(block_size=int(cfg.block_size), vocab_size=int(cfg.vocab_size), n_layer=int(cfg.n_layer),
                    n_head=int(cfg.n_head), hidden_size=int(cfg.hidden_size),
                    intermediate_size=int(cfg.intermediate_size), norm_eps=float(cfg.norm_eps),
                    eos_token_id=int(cfg.eos_token_id), pad_token_id=int(cfg.pad_token_id),
-                   predict_token_id=int(cfg.predict_token_id), window_size=int(cfg.window_size))
-    slots = (int(getattr(model, "_prediction_slot_index", 0)), int(getattr(model, "_window_slot_index", 0)),
-             int(getattr(model, "_retained_slot_index", 1)))
-    variant = next((name for name, v in _VARIANTS.items() if v[:3] == slots), None)
-    if variant is None:
-        raise ValueError(f"unknown slot assignment {slots}")
+                   predict_token_id=-1 if is_standard else int(cfg.predict_token_id),
+                   window_size=0 if is_standard else int(cfg.window_size))
+    if is_standard:
+        variant = "standard"
+    else:
+        slots = (int(getattr(model, "_prediction_slot_index", 0)), int(getattr(model, "_window_slot_index", 0)),
+                 int(getattr(model, "_retained_slot_index", 1)))
+        variant = next((name for name, v in _VARIANTS.items() if v[:3] == slots), None)
+        if variant is None:
+            raise ValueError(f"unknown slot assignment {slots}")
     sd = model.state_dict()
     first = next(iter(sd.values()))
     if param_dtype is None:

@@ -17,7 +17,9 @@ It imports, unmodified, from the reference:
     and the prefill -> decode hand-over     src/modeling/models/reverse_sps/inference.py:568-613
     through the reference's own tiny Delayed-State / SPS test models.
   * ``apply_rotary_emb``, ``precompute_freqs_cis``  src/modeling/models/model.py:134-230
-  * ``SPSModel`` / ``ReverseSPSModel`` themselves (src/modeling/models/sps/, reverse_sps/): dense
+  * the Standard ``Model`` (src/modeling/models/full_attention_model.py): prefill logits and its
+    own cached greedy ``generate`` on CPU.
+  * ``SPSModel`` / ``ReverseSPSModel`` / ``DelayedStateModel`` themselves (src/modeling/models/sps/, reverse_sps/): dense
     ``forward`` (its attention name rebound to the SDPA oracle above, since the Triton kernel needs
     a GPU), stepwise ``forward_efficient`` (with the eager cache updates) and greedy tokens
     obtained the way tests/models/sps/test_dense_only.py:212-249 obtains them.
@@ -363,6 +365,50 @@ def model_cases():
         OUT[f"model_{tag}_greedy_margin"] = torch.stack(margins, dim=1).numpy()
 
 
+def standard_model_cases():
+    """The reference's Standard model (full_attention_model.py) on CPU fp32: logits of its
+    generation prefill path over left-padded prompts with an EOS inside, and its own greedy
+    ``generate`` (cached decode), weights included."""
+    from modeling.models.full_attention_model import Model, ModelConfig
+    torch.manual_seed(47)
+    cfg = ModelConfig(block_size=32, vocab_size=64, n_layer=2, n_head=2, hidden_size=128,
+                      intermediate_size=256, dropout=0.0, bias=False, eos_token_id=63, pad_token_id=62)
+    model = Model(cfg).eval()
+    with torch.no_grad():
+        for prm in model.parameters():
+            if prm.dim() >= 2:
+                prm.mul_(6.0)
+            prm.copy_(prm.bfloat16().float())
+    for name, t in model.state_dict().items():
+        put(f"model_std_w__{name}", t)
+    put("model_std_dims", np.array([cfg.block_size, cfg.vocab_size, cfg.n_layer, cfg.n_head, cfg.hidden_size,
+                                     cfg.intermediate_size, cfg.eos_token_id, cfg.pad_token_id, -1, 0]))
+    g = torch.Generator().manual_seed(53)
+    padded = torch.randint(0, 60, (3, 10), generator=g)
+    padded[0, :3] = cfg.pad_token_id
+    padded[1, 5] = cfg.eos_token_id
+    padded[2, :6] = cfg.pad_token_id
+    padded[2, 7] = cfg.eos_token_id
+    put("model_std_padded_idx", padded)
+    hidden, _ = model._forward_generation_hidden_states(padded)
+    put("model_std_padded_logits", model.lm_head(hidden))
+    out = model.generate(padded, 8, do_sample=False, stop_on_eos=False)
+    put("model_std_greedy", out)
+    margins = []
+    for step in range(8):
+        seq = out[:, : padded.shape[1] + step]
+        z = model.lm_head(model._forward_generation_hidden_states(seq)[0])[:, -1].clone()
+        z[:, cfg.pad_token_id] = float("-inf")
+        top2 = z.topk(2, dim=-1).values
+        margins.append(top2[:, 0] - top2[:, 1])
+    OUT["model_std_greedy_margin"] = torch.stack(margins, dim=1).numpy()
+    # a prompt that ends on EOS: the decode cache starts empty (full_attention_model.py:703-705)
+    ends = torch.randint(0, 60, (2, 6), generator=g)
+    ends[0, -1] = cfg.eos_token_id
+    put("model_std_eos_end_idx", ends)
+    put("model_std_eos_end_greedy", model.generate(ends, 5, do_sample=False, stop_on_eos=False))
+
+
 if __name__ == "__main__":
     with torch.no_grad():
         sps_cases()
@@ -374,6 +420,7 @@ if __name__ == "__main__":
         cache_fill_cases()
         rope_cases()
         model_cases()
+        standard_model_cases()
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
     np.savez_compressed(path, **OUT)
     print(f"wrote {path}: {len(OUT)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")

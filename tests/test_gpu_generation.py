@@ -445,3 +445,62 @@ def test_left_padded_batch_matches_unpadded_rows(golden):
         out = solo_eng.generate(single, 4, stop_on_eos=False).cpu()
         assert torch.equal(batched[r, :first], torch.full((first,), pad))
         assert torch.equal(batched[r, first:], out[0]), r
+
+
+# ----------------------------------------------------------------------------- Standard model
+
+@pytest.mark.parametrize("split", [0, 7, 10])
+def test_standard_model_prefill_then_decode_matches_reference(golden, split):
+    """The Standard model (one row per token, cache = current document, q = 1 decode): logits of
+    a batched prefill of the first ``split`` columns and of the token-by-token decode of the rest
+    against the reference's own prefill path (full_attention_model.py:744-853), fp32 there."""
+    weights, fields = _golden_model(golden, "std")
+    eng = _engine(weights, fields, "standard", torch.float32)
+    idx = torch.from_numpy(golden["model_std_padded_idx"]).to(_dev())
+    ref = torch.from_numpy(golden["model_std_padded_logits"])
+    pad = fields["pad_token_id"]
+    b, t = idx.shape
+    got = {}
+    if split == 0:
+        state = eng.build_decode_state(b, t)
+    else:
+        state, logits = eng.prefill(idx[:, :split].clone(), max_new_tokens=t - split + 1)
+        got[split - 1] = logits.float().cpu()
+    for col in range(split, t):
+        got[col] = eng.decode_one_token(state, idx[:, col], idx[:, col] != pad).float().cpu()
+    for col, z in got.items():
+        real = (idx[:, col] != pad).cpu()
+        torch.testing.assert_close(z[real], ref[:, col][real], atol=8e-2, rtol=2e-2)
+        assert (z[real] - ref[:, col][real]).abs().mean().item() < 2e-2
+    full = eng.forward_logits(idx).float().cpu()      # dense path, positions 0..T-1: unpadded row only
+    torch.testing.assert_close(full[1], ref[1], atol=8e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_standard_model_greedy_tokens_match_reference(golden, use_graph):
+    weights, fields = _golden_model(golden, "std")
+    eng = _engine(weights, fields, "standard", torch.float32)
+    idx = torch.from_numpy(golden["model_std_padded_idx"])
+    ref = torch.from_numpy(golden["model_std_greedy"])
+    margin = torch.from_numpy(golden["model_std_greedy_margin"])
+    n_new = ref.shape[1] - idx.shape[1]
+    out = eng.generate(idx, n_new, stop_on_eos=False, use_graph=use_graph).cpu()
+    compared = 0
+    for r in range(idx.shape[0]):
+        for s in range(n_new):
+            if float(margin[r, s]) < 0.15:
+                break
+            assert int(out[r, idx.shape[1] + s]) == int(ref[r, idx.shape[1] + s]), (r, s)
+            compared += 1
+    assert compared >= 8
+    # a prompt that ends on EOS: the cache starts empty, the first new token opens a document
+    ends = torch.from_numpy(golden["model_std_eos_end_idx"])
+    want = torch.from_numpy(golden["model_std_eos_end_greedy"])
+    dims = mo.Dims(**fields)
+    _, margins = mo.generate(weights, dims, ends, 5, variant="standard", stop_on_eos=False, return_margins=True)
+    got = eng.generate(ends, 5, stop_on_eos=False, use_graph=use_graph).cpu()
+    for r in range(2):
+        for s in range(5):
+            if float(margins[r, s]) < 0.15:
+                break
+            assert int(got[r, 6 + s]) == int(want[r, 6 + s]), (r, s)

@@ -98,3 +98,23 @@ def test_document_ids_match_the_reference_known_answers(case):
     idx, want = (torch.tensor(x) for x in DOC_ID_CASES[case])
     assert torch.equal(mo.document_idx(idx, eos=E, pad=P), want)
     assert torch.equal(left_padded_document_idx(idx, E, P), want)
+
+
+def test_standard_model_logits_and_greedy_tokens_match_reference():
+    """The Standard model (no <predict> rows): prefill logits over left-padded prompts with an EOS
+    inside, its cached greedy decode, and a prompt that ends on EOS."""
+    weights, dims = golden_model("std")
+    idx = torch.from_numpy(G["model_std_padded_idx"])
+    pos = mo.left_padded_positions(idx, dims.pad_token_id)
+    got = mo.logits(weights, dims, idx, variant="standard", positions=pos, operand_dtype=torch.float32)
+    ref = torch.from_numpy(G["model_std_padded_logits"])
+    real = idx != dims.pad_token_id
+    assert (got - ref)[real].abs().max().item() < 2e-4
+    want = torch.from_numpy(G["model_std_greedy"])
+    out, margins = mo.generate(weights, dims, idx, 8, variant="standard", stop_on_eos=False,
+                               operand_dtype=torch.float32, return_margins=True)
+    assert torch.equal(out, want)
+    assert np.allclose(margins.numpy(), G["model_std_greedy_margin"], atol=1e-3)
+    ends = torch.from_numpy(G["model_std_eos_end_idx"])
+    out2 = mo.generate(weights, dims, ends, 5, variant="standard", stop_on_eos=False, operand_dtype=torch.float32)
+    assert torch.equal(out2, torch.from_numpy(G["model_std_eos_end_greedy"]))
