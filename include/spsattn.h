@@ -18,6 +18,8 @@
  *   spsattn_prefill_fwd      src/modeling/models/attention/triton_sps_flash_attention.py:491-620 (wrapper)
  *                            and :147-269 (_attn_fwd_sps); the reverse and standard variants
  *                            triton_reverse_sps_flash_attention.py:242-331, triton_full_flash_attention.py:204-283
+ *   spsattn_prefill_bwd      triton_sps_flash_attention.py:623-720 (backward wrapper), :272-488
+ *                            (_attn_bwd_preprocess, _sps_bwd_dkdv_kernel, _sps_bwd_dq_kernel)
  *   spsattn_decode_fwd       src/modeling/models/utils/decode_attention.py:483-594 (q=2), :393-480 (q=1)
  *   spsattn_kv_update        src/modeling/models/utils/decode_attention_fast.py:139-221
  *   spsattn_fill_decode_caches  src/modeling/models/reverse_sps/inference.py:568-613
@@ -112,6 +114,25 @@ int spsattn_prefill_fwd_strided(const void* q, const void* k, const void* v, voi
                                 int mask_flags,
                                 void* workspace, size_t workspace_bytes,
                                 int* device_status, void* stream);
+
+/* Backward of spsattn_prefill_fwd (the training path): dq, dk, dv from d_o, with the
+ * probabilities recomputed from `lse` as written by the forward call on the same q, k, v, mask and
+ * sm_scale (the reference's backward, triton_sps_flash_attention.py:623-720, does the same with
+ * its M tensor).  All tensors dense [B, H, N, D] of `dtype`; `o` is the forward output; lse is
+ * [B, H, N] fp32.  Three launches: delta = rowsum(d_o * o), then dk / dv (one block per 128-token
+ * key tile of each parity stream, visiting only the query tiles that can see it), then dq (one
+ * block per 128-row query tile, visiting the key tiles the forward visits).  D in {64, 128};
+ * N <= 65536.  workspace: spsattn_prefill_bwd_workspace_bytes(B, H, N, D) bytes, 256-byte aligned. */
+size_t spsattn_prefill_bwd_workspace_bytes(int B, int H, int N, int D);
+
+int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                        const float* lse, void* dq, void* dk, void* dv,
+                        const void* doc_ids, int doc_is_i64, int64_t doc_stride_b, int64_t doc_stride_t,
+                        int B, int H, int N, int D, int dtype, float sm_scale,
+                        int persistent_parity, int temporary_window, int persistent_window,
+                        int mask_flags,
+                        void* workspace, size_t workspace_bytes,
+                        int* device_status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Decode: nq (1 or 2) queries per (sequence, head) over up to 3 length-masked KV segments plus up

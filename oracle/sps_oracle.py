@@ -214,6 +214,54 @@ def prefill_attention(
     return (out, lse) if return_lse else out
 
 
+def prefill_attention_grads(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    d_o: torch.Tensor,
+    sm_scale: float,
+    *,
+    persistent_parity: int = PARITY_EVEN,
+    temporary_window: int = 0,
+    persistent_window: Optional[int] = None,
+    docs: Optional[torch.Tensor] = None,
+    mask_flags: int = 0,
+):
+    """dQ, dK, dV of ``prefill_attention`` in fp32 on CPU, one (batch, head) slice at a time.
+
+    The closed form every flash-attention backward uses, and the one the reference's kernels
+    implement (src/modeling/models/attention/triton_sps_flash_attention.py:272-488):
+    P = softmax(mask(S)), dV = P^T dO, dP = dO V^T, dS = P * (dP - rowsum(dO * O)),
+    dQ = dS K * scale, dK = dS^T Q * scale.  The reference's own test obtains the same
+    quantities from autograd through its SDPA oracle
+    (src/modeling/tests/attention/triton/test_sps_attention.py:79-131); the CPU tests check
+    this function against exactly that.
+    """
+    B, H, N, D = q.shape
+    qf, kf, vf, gf = q.float(), k.float(), v.float(), d_o.float()
+    dq, dk, dv = torch.zeros_like(qf), torch.zeros_like(kf), torch.zeros_like(vf)
+    sel = np.arange(N)
+    for b in range(B):
+        drow = None if docs is None else docs[b].cpu().numpy()
+        vis = torch.from_numpy(_visible_rows(N, sel, persistent_parity, temporary_window,
+                                             persistent_window, drow, mask_flags))
+        for h in range(H):
+            s = (qf[b, h] @ kf[b, h].T) * float(sm_scale)
+            s = s.masked_fill(~vis, float("-inf"))
+            m = s.max(dim=1, keepdim=True).values
+            m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+            p = torch.exp(s - m)
+            l = p.sum(dim=1, keepdim=True)
+            p = p / torch.where(l > 0, l, torch.ones_like(l))
+            o = p @ vf[b, h]
+            dv[b, h] = p.T @ gf[b, h]
+            dp = gf[b, h] @ vf[b, h].T
+            ds = p * (dp - (gf[b, h] * o).sum(dim=1, keepdim=True))
+            dq[b, h] = (ds @ kf[b, h]) * float(sm_scale)
+            dk[b, h] = (ds.T @ qf[b, h]) * float(sm_scale)
+    return dq, dk, dv
+
+
 def _visible_rows(n, sel, parity, w, pw, drow, flags) -> np.ndarray:
     i = sel.astype(np.int64)[:, None]
     j = np.arange(n, dtype=np.int64)[None, :]

@@ -4,8 +4,10 @@
 same arguments, in the same order and with the same meaning, as the reference's
 src/modeling/models/attention/triton_sps_flash_attention.py:725-753,
 triton_reverse_sps_flash_attention.py:827-853 and triton_full_flash_attention.py:679-709, so the
-model classes can call them unchanged (see ``sps_b200.install``).  They are forward only.
-All compute happens in libspsattn.so (tcgen05 / TMA kernel for head_dim 64 and 128).
+model classes can call them unchanged (see ``sps_b200.install``).  For head_dim 64 and 128 they
+are differentiable like the reference's ``torch.autograd.Function``s (backward:
+triton_sps_flash_attention.py:623-720); the other head dims are forward only.
+All compute happens in libspsattn.so (tcgen05 / TMA kernels for head_dim 64 and 128).
 """
 
 from __future__ import annotations
@@ -54,11 +56,90 @@ def _addressable(t: torch.Tensor) -> bool:
             all(s % 8 == 0 and s >= D for s in t.stride()[:3]))
 
 
+_BACKWARD_HEAD_DIMS = (64, 128)
+
+
+def _needs_grad(*tensors) -> bool:
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+
+
 def _forward_only(*tensors) -> None:
-    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+    if _needs_grad(*tensors):
         raise RuntimeError(
-            "sps_b200 attention is forward only: call it under torch.no_grad() / inference_mode(), "
-            "or detach the inputs (the backward kernels are not part of this library)")
+            "this sps_b200 call is forward only: call it under torch.no_grad() / inference_mode(), "
+            "or detach the inputs (backward kernels exist for prefill attention with head_dim 64 "
+            "and 128 only)")
+
+
+def _docs_args(documents_idx, B, N, device):
+    """(tensor kept alive, pointer, is_int64, batch stride, token stride) of a document-id tensor."""
+    if documents_idx is None:
+        return None, None, 0, 0, 0
+    docs = documents_idx
+    assert docs.shape[0] == B and docs.shape[1] == N
+    assert docs.is_cuda and docs.device == device
+    if docs.dtype not in (torch.int64, torch.int32):
+        docs = docs.to(torch.int64)
+    sb, st = docs.stride()
+    return docs, docs.data_ptr(), int(docs.dtype == torch.int64), sb, st
+
+
+def prefill_attention_backward(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
+    d_o: torch.Tensor, sm_scale: float, *, persistent_parity: int, temporary_window: int = 0,
+    persistent_window: Optional[int] = None, documents_idx: Optional[torch.Tensor] = None,
+    mask_flags: int = 0,
+):
+    """dQ, dK, dV of ``prefill_attention`` from dO, the forward output ``o`` and its ``lse``
+    (the reference's backward: triton_sps_flash_attention.py:623-720).  head_dim 64 or 128."""
+    lib = _lib.load()
+    B, H, N, D = q.shape
+    if D not in _BACKWARD_HEAD_DIMS:
+        raise RuntimeError(f"the backward kernels cover head_dim {_BACKWARD_HEAD_DIMS}, got {D}")
+    dt = _dtype_code(q)
+    q, k, v, o, d_o = (x.contiguous() for x in (q, k, v, o, d_o.to(q.dtype)))
+    lse = lse.contiguous()
+    assert lse.shape == (B, H, N) and lse.dtype == torch.float32
+    docs, docs_ptr, docs_i64, sb, st = _docs_args(documents_idx, B, N, q.device)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ws_bytes = lib.spsattn_prefill_bwd_workspace_bytes(B, H, N, D)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    pw = _lib.NO_WINDOW if persistent_window is None else max(-1, min(int(persistent_window), N))
+    with torch.cuda.device(q.device):
+        rc = lib.spsattn_prefill_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), docs_ptr, docs_i64, sb, st, B, H, N, D, dt,
+            float(sm_scale), int(persistent_parity), max(-1, min(int(temporary_window), N)), pw,
+            int(mask_flags), ws.data_ptr(), ws_bytes, _status(q.device).data_ptr(),
+            torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "spsattn_prefill_bwd")
+    del docs
+    return dq, dk, dv
+
+
+class _PrefillAttention(torch.autograd.Function):
+    """Differentiable prefill attention: forward and backward both run in libspsattn.so."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, sm_scale, persistent_parity, temporary_window, persistent_window,
+                documents_idx, mask_flags):
+        o, lse = _prefill_forward(q, k, v, sm_scale, persistent_parity=persistent_parity,
+                                  temporary_window=temporary_window, persistent_window=persistent_window,
+                                  documents_idx=documents_idx, mask_flags=mask_flags, return_lse=True)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.docs = documents_idx
+        ctx.args = (float(sm_scale), int(persistent_parity), int(temporary_window), persistent_window,
+                    int(mask_flags))
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        sm_scale, parity, tw, pw, flags = ctx.args
+        dq, dk, dv = prefill_attention_backward(
+            q, k, v, o, lse, d_o, sm_scale, persistent_parity=parity, temporary_window=tw,
+            persistent_window=pw, documents_idx=ctx.docs, mask_flags=flags)
+        return dq, dk, dv, None, None, None, None, None, None
 
 
 def prefill_attention(
@@ -79,11 +160,24 @@ def prefill_attention(
 
     ``persistent_parity``: 0 (SPS), 1 (Reverse-SPS / Delayed-State) or -1 (Standard).
     Returns O (same dtype as q) and, with ``return_lse``, the base-2 log-sum-exp [B, H, N] fp32.
+    When an input requires grad (head_dim 64 or 128) the result is differentiable.
     """
+    if _needs_grad(q, k, v):
+        if q.shape[-1] not in _BACKWARD_HEAD_DIMS or return_lse or out is not None:
+            _forward_only(q, k, v)
+        return _PrefillAttention.apply(q, k, v, sm_scale, persistent_parity, temporary_window,
+                                       persistent_window, documents_idx, mask_flags)
+    return _prefill_forward(q, k, v, sm_scale, persistent_parity=persistent_parity,
+                            temporary_window=temporary_window, persistent_window=persistent_window,
+                            documents_idx=documents_idx, mask_flags=mask_flags, return_lse=return_lse,
+                            out=out)
+
+
+def _prefill_forward(q, k, v, sm_scale, *, persistent_parity, temporary_window=0, persistent_window=None,
+                     documents_idx=None, mask_flags=0, return_lse=False, out=None):
     lib = _lib.load()
     if not q.is_cuda:
         raise RuntimeError("sps_b200 attention needs CUDA tensors; there is no CPU path")
-    _forward_only(q, k, v)
     B, H, N, D = q.shape
     assert k.shape == q.shape and v.shape == q.shape, "q, k, v must have the same shape"
     assert k.dtype == q.dtype and v.dtype == q.dtype, "q, k, v must have the same dtype"

@@ -1,0 +1,609 @@
+// Backward of the SPS prefill attention for sm_100a: dQ, dK, dV from dO, with the probabilities
+// recomputed from the saved log-sum-exp (no [N, N] tensor is ever stored).
+//
+// Three launches, like the reference's backward (src/modeling/models/attention/
+// triton_sps_flash_attention.py:623-720: `_attn_bwd_preprocess`, `_sps_bwd_dkdv_kernel`,
+// `_sps_bwd_dq_kernel`):
+//   delta_kernel      delta[i] = sum_d dO[i,d] * O[i,d]
+//   bwd kernel, kDQ   one block per 128-row query tile; streams the key tiles the forward
+//                     kernel visits for that tile:  dQ += dS K
+//   bwd kernel, kDKV  one block per 128-token key tile of one parity stream; streams the 64-row
+//                     query tiles that can see it:  dV += P^T dO,  dK += dS^T Q
+// Both modes are the same pipeline with the operands renamed.  With X the stationary pair of
+// 128-row tiles and Y the streamed pair of 64-row tiles:
+//   S  = X0 Y0^T   (Q K^T, or its transpose K Q^T)        tcgen05.mma 128x64xD into TMEM
+//   dP = X1 Y1^T   (dO V^T, or V dO^T)                    tcgen05.mma 128x64xD into TMEM
+//   P  = exp2(S * scale*log2e - lse),  dS = P * (dP - delta) * scale     softmax warps, registers
+//   acc0 += dS Y0  (dQ += dS K,  or dK += dS^T Q)         tcgen05.mma 128xDx64, Y as MN-major B
+//   acc1 += P  Y1  (kDKV only: dV += P^T dO)
+// The visibility rule is the forward's: every mask bit comes from row_interval().
+#pragma once
+
+#include "common.cuh"
+#include "mask.cuh"
+#include "prefill_sm100.cuh"
+
+namespace spsattn {
+
+constexpr int kBwdDQ = 0;
+constexpr int kBwdDKV = 1;
+constexpr int kBwdThreads = 192;
+constexpr int kBwdTable = 1024;      // streamed tiles listed per block (64K rows in kDKV mode)
+
+struct BwdParams {
+  void* out0;            // kDQ: dQ, kDKV: dK   dense [B, H, N, D]
+  void* out1;            // kDKV: dV
+  const float* lse;      // [B, H, N], log2 domain (as written by the forward kernel)
+  const float* delta;    // [B, H, N]
+  const void* docs;
+  int64_t doc_stride_b, doc_stride_t;
+  int doc_is_i64;
+  const int* lo;
+  const int* mono;
+  int B, H, N;
+  int n_xtiles;          // stationary tiles per (batch, head)
+  MaskParams mask;
+  float scale_log2;
+  float sm_scale;
+  int* status;
+};
+
+template <int D>
+struct BwdCfg {
+  static constexpr int kStages = 2;
+  static constexpr int kXBytes = 128 * D * 2;
+  static constexpr int kXSub = 128 * 128;
+  static constexpr int kYBytes = 64 * D * 2;
+  static constexpr int kYSub = 64 * 128;
+  static constexpr int kPBytes = 128 * 64 * 2;
+  static constexpr int kOffX0 = 0;
+  static constexpr int kOffX1 = kXBytes;
+  static constexpr int kOffY = 2 * kXBytes;                    // [stage][Y0 | Y1]
+  static constexpr int kOffP = kOffY + kStages * 2 * kYBytes;
+  static constexpr int kOffDS = kOffP + kPBytes;
+  static constexpr int kOffBar = kOffDS + kPBytes;
+  static constexpr int kSmemBytes = kOffBar + 256 + 1024;
+  static constexpr uint32_t kColS = 0, kColDP = 64, kColAcc0 = 128, kColAcc1 = 128 + D;
+  static constexpr uint32_t kTmemCols = (D == 64) ? 256 : 512;
+  static constexpr int kBlocksPerSM = (D == 64) ? 2 : 1;
+};
+
+// delta[b, h, i] = sum_d dO * O: one warp per row of dense [B*H*N, D] operands
+template <bool FP16>
+__global__ void __launch_bounds__(256)
+bwd_delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float* __restrict__ delta,
+                 long long rows, int D) {
+  const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const uint32_t* po = reinterpret_cast<const uint32_t*>(o) + r * (D / 2);
+  const uint32_t* pd = reinterpret_cast<const uint32_t*>(d_o) + r * (D / 2);
+  float acc = 0.f;
+  for (int x = lane; x < D / 2; x += 32) {
+    float a0, a1, b0, b1;
+    unpack2<FP16>(po[x], a0, a1);
+    unpack2<FP16>(pd[x], b0, b1);
+    acc = fmaf(a0, b0, fmaf(a1, b1, acc));
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[r] = acc;
+}
+
+struct BwdMeta {           // per streamed query tile in kDKV mode: one entry per column
+  float lse[64];
+  float delta[64];
+  int kmin[64];
+  int kmax[64];
+  long long doc[64];
+};
+
+template <int D, bool FP16, int MODE>
+__global__ void __launch_bounds__(kBwdThreads, BwdCfg<D>::kBlocksPerSM)
+prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__ CUtensorMap tm_x1,
+                         const __grid_constant__ CUtensorMap tm_y0, const __grid_constant__ CUtensorMap tm_y1,
+                         const BwdParams prm) {
+  using Cfg = BwdCfg<D>;
+  constexpr bool kDKV = MODE == kBwdDKV;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ BlockPlan s_plan;          // kDQ: the forward's key-tile plan of this query tile
+  __shared__ int s_tiles[kBwdTable];    // kDQ: packed key tiles; kDKV: (query tile << 1) | masked
+  __shared__ int s_ntiles;
+  __shared__ int s_cand[2];             // kDKV: first candidate query tile, number of candidates
+  __shared__ BwdMeta s_meta[kDKV ? 2 : 1];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  const int bh = blockIdx.x / prm.n_xtiles;
+  const int xt_raw = blockIdx.x % prm.n_xtiles;
+  const int b = bh / prm.H;
+  const int h = bh - b * prm.H;
+  const int ks = prm.mask.ks;
+  const int Tk = prm.N / ks;                       // key tokens per stream
+  // kDQ: late query tiles are the heavy ones, kDKV: early key tiles are: both go first
+  const int xt = kDKV ? xt_raw : prm.n_xtiles - 1 - xt_raw;
+  const int stream = kDKV ? (ks == 2 ? (xt & 1) : 0) : 0;
+  const int x0 = kDKV ? (xt / ks) * 128 : xt * 128;   // first key token / first query row
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sX0 = smem_base + Cfg::kOffX0;
+  const uint32_t sX1 = smem_base + Cfg::kOffX1;
+  const uint32_t sY = smem_base + Cfg::kOffY;
+  const uint32_t sP = smem_base + Cfg::kOffP;
+  const uint32_t sDS = smem_base + Cfg::kOffDS;
+  const uint32_t bar0 = smem_base + Cfg::kOffBar;
+  const uint32_t bar_x_full = bar0;
+  const uint32_t bar_y_full = bar0 + 8;      // [2]
+  const uint32_t bar_y_empty = bar0 + 24;    // [2]
+  const uint32_t bar_s_full = bar0 + 40;
+  const uint32_t bar_s_free = bar0 + 48;
+  const uint32_t bar_p_full = bar0 + 56;
+  const uint32_t bar_acc_done = bar0 + 64;
+  const uint32_t bar_meta = bar0 + 72;       // [2]
+
+  const bool has_docs = prm.docs != nullptr;
+  const bool general = has_docs && prm.mono != nullptr && prm.mono[b] == 0;
+  const int* lo_b = (has_docs && !general) ? prm.lo + (size_t)b * prm.N : nullptr;
+
+  if (tid == 0) {
+    s_abort = (prm.status != nullptr && *reinterpret_cast<volatile int*>(prm.status) != 0) ? 1 : 0;
+    if constexpr (!kDKV) {
+      BlockPlan bp;
+      bp.general_docs = general ? 1 : 0;
+      int lo0 = 0, lo1 = 0;
+      if (lo_b != nullptr) {
+        lo0 = lo_b[x0];
+        lo1 = lo_b[min(x0 + 127, prm.N - 1)];
+      }
+      if (ks == 1) {
+        bp.n_streams = 1;
+        bp.stream_id[0] = 0;
+        bp.stream_id[1] = 0;
+        bp.sp[0] = plan_stream(prm.mask, x0, lo0, lo1, 0, kTileN);
+        bp.sp[1] = bp.sp[0];
+        bp.sp[1].ntiles = 0;
+      } else {
+        bp.n_streams = 2;
+        bp.stream_id[0] = prm.mask.pp;
+        bp.stream_id[1] = 1 - prm.mask.pp;
+        bp.sp[0] = plan_stream(prm.mask, x0, lo0, lo1, bp.stream_id[0], kTileN);
+        bp.sp[1] = plan_stream(prm.mask, x0, lo0, lo1, bp.stream_id[1], kTileN);
+      }
+      bp.n_tiles = bp.sp[0].ntiles + bp.sp[1].ntiles;
+      s_plan = bp;
+      s_ntiles = bp.n_tiles;
+    } else {
+      // query rows that can see some key of this tile: from the first key's own row up to the
+      // window / document limit of the last key
+      const int kl = min(x0 + 127, Tk - 1);
+      const int jr_first = ks * x0 + stream;
+      const int jr_last = ks * kl + stream;
+      long long i_hi = prm.N - 1;
+      if (ks == 2) {
+        if (stream == prm.mask.pp) {
+          if (prm.mask.has_pw) i_hi = min(i_hi, 2ll * (kl + max(prm.mask.pw, 0)) + 1);
+        } else {
+          i_hi = min(i_hi, 2ll * (kl + max(prm.mask.w, 0)) + 1);
+        }
+      }
+      if (lo_b != nullptr) {
+        // first row after jr_last that starts a later run (lo is a non-decreasing step function)
+        int a = jr_last + 1, c = prm.N;
+        while (a < c) {
+          const int mid = (a + c) >> 1;
+          if (lo_b[mid] > jr_last) c = mid; else a = mid + 1;
+        }
+        i_hi = min(i_hi, (long long)a - 1);
+      }
+      int first = jr_first / 64, n = 0;
+      if (x0 < Tk && i_hi >= jr_first) n = min((int)(i_hi / 64) - first + 1, kBwdTable);
+      s_cand[0] = first;
+      s_cand[1] = n;
+    }
+  }
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_init(bar_x_full, 1);
+      for (int s = 0; s < 2; ++s) {
+        mbar_init(bar_y_full + 8 * s, 1);
+        mbar_init(bar_y_empty + 8 * s, 1);
+        mbar_init(bar_meta + 8 * s, 64);
+      }
+      mbar_init(bar_s_full, 1);
+      mbar_init(bar_s_free, 128);
+      mbar_init(bar_p_full, 128);
+      mbar_init(bar_acc_done, 1);
+      fence_barrier_init();
+      tma_prefetch_desc(&tm_x0);
+      tma_prefetch_desc(&tm_x1);
+      mbar_arrive_expect_tx(bar_x_full, 2 * Cfg::kXBytes);
+      for (int c = 0; c < D / 64; ++c) {
+        if constexpr (kDKV) {
+          for (int half = 0; half < 2; ++half) {
+            tma_load_5d(sX0 + c * Cfg::kXSub + half * 8192, &tm_x0, bar_x_full, c * 64, stream,
+                        x0 + 64 * half, h, b);
+            tma_load_5d(sX1 + c * Cfg::kXSub + half * 8192, &tm_x1, bar_x_full, c * 64, stream,
+                        x0 + 64 * half, h, b);
+          }
+        } else {
+          tma_load_4d(sX0 + c * Cfg::kXSub, &tm_x0, bar_x_full, c * 64, x0, h, b);
+          tma_load_4d(sX1 + c * Cfg::kXSub, &tm_x1, bar_x_full, c * 64, x0, h, b);
+        }
+      }
+      tma_prefetch_desc(&tm_y0);
+      tma_prefetch_desc(&tm_y1);
+    }
+    __syncwarp();
+    tmem_alloc<Cfg::kTmemCols>(smem_u32(&s_tmem_base));
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+
+  // ---- the list of streamed tiles
+  if constexpr (!kDKV) {
+    for (int j = tid; j < min(s_plan.n_tiles, kBwdTable); j += kBwdThreads)
+      s_tiles[j] = pack_tile(tile_info(s_plan, j));
+  } else {
+    // per candidate query tile: does any row see any key of this tile, do all rows see all keys
+    const int first = s_cand[0], n_cand = s_cand[1];
+    for (int cnd = warp; cnd < n_cand; cnd += kBwdThreads / 32) {
+      const int q0 = (first + cnd) * 64;
+      bool any = false, all = true;
+      for (int rr = lane; rr < 64; rr += 32) {
+        const int i = q0 + rr;
+        int kmin = 0, kmax = -1;
+        if (i < prm.N) row_interval(prm.mask, i, lo_b != nullptr ? lo_b[i] : 0, stream, kmin, kmax);
+        any |= max(kmin, x0) <= min(kmax, x0 + 127);
+        all &= kmin <= x0 && kmax >= x0 + 127;
+      }
+      any = __any_sync(0xffffffffu, any);
+      all = __all_sync(0xffffffffu, all);
+      if (lane == 0) s_tiles[cnd] = any ? (((first + cnd) << 1) | ((all && !general) ? 0 : 1)) : -1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int n = 0;
+      for (int cnd = 0; cnd < n_cand; ++cnd) {
+        const int e = s_tiles[cnd];
+        if (e >= 0) s_tiles[n++] = e;
+      }
+      s_ntiles = n;
+    }
+  }
+  __syncthreads();
+  const int n_tiles = s_ntiles;
+  volatile int* abort_flag = &s_abort;
+  const bool bail = s_abort != 0;
+
+  auto dq_tile = [&](int j) {
+    return j < kBwdTable ? unpack_tile(s_tiles[j]) : tile_info(s_plan, j);
+  };
+
+  if (!bail && n_tiles > 0) {
+    if (warp == 4) {
+      // ------------------------------------------------------------------ TMA producer
+      bool ok = true;
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int st = j % Cfg::kStages;
+        if (j >= Cfg::kStages)
+          ok = warp_wait(bar_y_empty + 8 * st, ((j / Cfg::kStages) - 1) & 1, abort_flag, prm.status);
+        if (!ok) break;
+        if (elect_one()) {
+          const uint32_t dst0 = sY + st * 2 * Cfg::kYBytes, dst1 = dst0 + Cfg::kYBytes;
+          mbar_arrive_expect_tx(bar_y_full + 8 * st, 2 * Cfg::kYBytes);
+          if constexpr (kDKV) {
+            const int q0 = (s_tiles[j] >> 1) * 64;
+            for (int c = 0; c < D / 64; ++c) {
+              tma_load_4d(dst0 + c * Cfg::kYSub, &tm_y0, bar_y_full + 8 * st, c * 64, q0, h, b);
+              tma_load_4d(dst1 + c * Cfg::kYSub, &tm_y1, bar_y_full + 8 * st, c * 64, q0, h, b);
+            }
+          } else {
+            const TileInfo t = dq_tile(j);
+            for (int c = 0; c < D / 64; ++c) {
+              tma_load_5d(dst0 + c * Cfg::kYSub, &tm_y0, bar_y_full + 8 * st, c * 64, t.stream, t.k0, h, b);
+              tma_load_5d(dst1 + c * Cfg::kYSub, &tm_y1, bar_y_full + 8 * st, c * 64, t.stream, t.k0, h, b);
+            }
+          }
+        }
+        __syncwarp();
+      }
+    } else if (warp == 5) {
+      // ------------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc_s = make_idesc_f16(FP16, 128, 64, false, false);
+      constexpr uint32_t idesc_acc = make_idesc_f16(FP16, 128, D, false, true);
+      const uint64_t dx0 = make_smem_desc_sw128(sX0, 16, 1024);
+      const uint64_t dx1 = make_smem_desc_sw128(sX1, 16, 1024);
+      const uint64_t dyk = make_smem_desc_sw128(sY, 16, 1024);               // Y as K-major B
+      const uint64_t dym = make_smem_desc_sw128(sY, Cfg::kYSub, 1024);       // Y as MN-major B
+      const uint64_t dp = make_smem_desc_sw128(sP, 16, 1024);
+      const uint64_t dds = make_smem_desc_sw128(sDS, 16, 1024);
+      const uint32_t dx0_lo = (uint32_t)dx0, dx1_lo = (uint32_t)dx1, dx_hi = (uint32_t)(dx0 >> 32);
+      const uint32_t dyk_lo = (uint32_t)dyk, dyk_hi = (uint32_t)(dyk >> 32);
+      const uint32_t dym_lo = (uint32_t)dym, dym_hi = (uint32_t)(dym >> 32);
+      const uint32_t dp_lo = (uint32_t)dp, dds_lo = (uint32_t)dds, dp_hi = (uint32_t)(dp >> 32);
+      auto issue_s = [&](int j) {
+        const int st = j % Cfg::kStages;
+        if (!warp_wait(bar_y_full + 8 * st, (j / Cfg::kStages) & 1, abort_flag, prm.status)) return false;
+        if (j >= 1) {
+          if (!warp_wait(bar_s_free, (j - 1) & 1, abort_flag, prm.status)) return false;
+        }
+        tc_fence_after();
+        const uint32_t y0 = dyk_lo + ((st * 2 * Cfg::kYBytes) >> 4);
+        const uint32_t y1 = y0 + (Cfg::kYBytes >> 4);
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t xa = ((kk / 4) * Cfg::kXSub + (kk % 4) * 32) >> 4;
+            const uint32_t yb = ((kk / 4) * Cfg::kYSub + (kk % 4) * 32) >> 4;
+            if (kk == 0) umma_ss<false>(tmem + Cfg::kColS, dx0_lo + xa, dx_hi, y0 + yb, dyk_hi, idesc_s);
+            else umma_ss<true>(tmem + Cfg::kColS, dx0_lo + xa, dx_hi, y0 + yb, dyk_hi, idesc_s);
+          }
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t xa = ((kk / 4) * Cfg::kXSub + (kk % 4) * 32) >> 4;
+            const uint32_t yb = ((kk / 4) * Cfg::kYSub + (kk % 4) * 32) >> 4;
+            if (kk == 0) umma_ss<false>(tmem + Cfg::kColDP, dx1_lo + xa, dx_hi, y1 + yb, dyk_hi, idesc_s);
+            else umma_ss<true>(tmem + Cfg::kColDP, dx1_lo + xa, dx_hi, y1 + yb, dyk_hi, idesc_s);
+          }
+          umma_commit(bar_s_full);
+        }
+        __syncwarp();
+        return true;
+      };
+      bool ok = warp_wait(bar_x_full, 0, abort_flag, prm.status);
+      if (ok) ok = issue_s(0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) ok = issue_s(j + 1);
+        if (!ok) break;
+        const int st = j % Cfg::kStages;
+        if (!warp_wait(bar_p_full, j & 1, abort_flag, prm.status)) break;
+        tc_fence_after();
+        const uint32_t y0 = dym_lo + ((st * 2 * Cfg::kYBytes) >> 4);
+        const uint32_t y1 = y0 + (Cfg::kYBytes >> 4);
+        if (elect_one()) {
+          // dS (and P): K-major A, 16 of the 64 streamed rows = 32 bytes per step; Y: MN-major B,
+          // 16 rows = 2048 bytes per step
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            if (j == 0 && kk == 0)
+              umma_ss<false>(tmem + Cfg::kColAcc0, dds_lo + ((kk * 32) >> 4), dp_hi, y0 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
+            else
+              umma_ss<true>(tmem + Cfg::kColAcc0, dds_lo + ((kk * 32) >> 4), dp_hi, y0 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
+          }
+          if constexpr (kDKV) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              if (j == 0 && kk == 0)
+                umma_ss<false>(tmem + Cfg::kColAcc1, dp_lo + ((kk * 32) >> 4), dp_hi, y1 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
+              else
+                umma_ss<true>(tmem + Cfg::kColAcc1, dp_lo + ((kk * 32) >> 4), dp_hi, y1 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
+            }
+          }
+          umma_commit(bar_acc_done);
+          umma_commit(bar_y_empty + 8 * st);
+        }
+        __syncwarp();
+      }
+    } else {
+      // ------------------------------------------------------------------ softmax warps
+      const int row = tid;                            // TMEM lane, row of the stationary tile
+      const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+      const float c = prm.scale_log2;
+      const float scale = prm.sm_scale;
+      const uint8_t* docs_b = nullptr;
+      if (general)
+        docs_b = reinterpret_cast<const uint8_t*>(prm.docs) + (size_t)b * prm.doc_stride_b * (prm.doc_is_i64 ? 8 : 4);
+      auto doc_at = [&](int r) -> long long {
+        const size_t off = (size_t)r * prm.doc_stride_t;
+        return prm.doc_is_i64 ? reinterpret_cast<const long long*>(docs_b)[off]
+                              : (long long)reinterpret_cast<const int*>(docs_b)[off];
+      };
+      // per-row constants
+      float neg_lse = 0.f, delta_i = 0.f;             // kDQ: this query row
+      int kmin_s[2] = {0, 0}, kmax_s[2] = {-1, -1};   // kDQ: visible key tokens per stream
+      long long my_doc = 0;
+      const int my_row = kDKV ? ks * (x0 + row) + stream : x0 + row;   // row in the sequence
+      const bool my_valid = kDKV ? (x0 + row < Tk) : (my_row < prm.N);
+      if constexpr (!kDKV) {
+        if (my_valid) {
+          neg_lse = -prm.lse[(size_t)bh * prm.N + my_row];
+          delta_i = prm.delta[(size_t)bh * prm.N + my_row];
+        }
+        const int lo_i = (lo_b != nullptr && my_valid) ? lo_b[my_row] : 0;
+        row_interval(prm.mask, my_row, lo_i, 0, kmin_s[0], kmax_s[0]);
+        row_interval(prm.mask, my_row, lo_i, 1, kmin_s[1], kmax_s[1]);
+      }
+      if (general && my_valid) my_doc = doc_at(my_row);
+      const int my_kt = x0 + row;                     // kDKV: this thread's key token
+      bool ok = true;
+
+      for (int j = 0; j < n_tiles; ++j) {
+        bool masked;
+        int y_first = 0, y_stream = 0;                // kDQ: first key token and stream of the tile
+        const BwdMeta* meta = &s_meta[0];
+        if constexpr (kDKV) {
+          const int e = s_tiles[j];
+          masked = (e & 1) != 0;
+          const int q0 = (e >> 1) * 64;
+          BwdMeta* mw = &s_meta[j & 1];
+          meta = mw;
+          if (tid < 64) {
+            const int i = q0 + tid;
+            float l = 0.f, dl = 0.f;
+            int kmin = 0, kmax = -1;
+            long long dd = 0;
+            if (i < prm.N) {
+              l = prm.lse[(size_t)bh * prm.N + i];
+              dl = prm.delta[(size_t)bh * prm.N + i];
+              row_interval(prm.mask, i, lo_b != nullptr ? lo_b[i] : 0, stream, kmin, kmax);
+              if (general) dd = doc_at(i);
+            }
+            mw->lse[tid] = -l;
+            mw->delta[tid] = dl;
+            mw->kmin[tid] = kmin;
+            mw->kmax[tid] = kmax;
+            mw->doc[tid] = dd;
+            mbar_arrive(bar_meta + 8 * (j & 1));
+          }
+          if (!mbar_wait(bar_meta + 8 * (j & 1), (j >> 1) & 1, abort_flag, prm.status)) {
+            ok = false;
+            break;
+          }
+        } else {
+          const TileInfo t = dq_tile(j);
+          masked = t.masked != 0;
+          y_first = t.k0;
+          y_stream = t.stream;
+        }
+        if (!mbar_wait(bar_s_full, j & 1, abort_flag, prm.status)) {
+          ok = false;
+          break;
+        }
+        if (j > 0) {   // P / dS buffers are free once the previous accumulation is done
+          if (!mbar_wait(bar_acc_done, (j - 1) & 1, abort_flag, prm.status)) {
+            ok = false;
+            break;
+          }
+        }
+        tc_fence_after();
+
+        // kDQ: the visible keys of this row form an interval of the tile's 64 columns
+        uint32_t vis_w[2] = {0xffffffffu, 0xffffffffu};
+        if constexpr (!kDKV) {
+          if (masked) {
+            const int cmin = max(kmin_s[y_stream] - y_first, 0);
+            const int cmax = min(kmax_s[y_stream] - y_first, 63);
+            const unsigned long long vis =
+                cmin > cmax ? 0ull : ((~0ull >> (63 - cmax)) & (~0ull << cmin));
+            vis_w[0] = (uint32_t)vis;
+            vis_w[1] = (uint32_t)(vis >> 32);
+            if (general) {
+#pragma unroll
+              for (int q4 = 0; q4 < 2; ++q4) {
+                uint32_t bits = 0;
+                for (int e = 0; e < 32; ++e) {
+                  const int jrow = ks * (y_first + q4 * 32 + e) + y_stream;
+                  if (jrow >= 0 && jrow < prm.N) bits |= (doc_at(jrow) == my_doc ? 1u : 0u) << e;
+                }
+                vis_w[q4] &= bits;
+              }
+            }
+          }
+        }
+
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t rs[32], rd[32];
+          tmem_ld32(tmem + lane_addr + Cfg::kColS + half * 32, rs);
+          tmem_ld32(tmem + lane_addr + Cfg::kColDP + half * 32, rd);
+          tmem_wait_ld();
+          if (half == 1) {
+            tc_fence_before();
+            mbar_arrive(bar_s_free);
+          }
+          uint32_t pk_p[16], pk_ds[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float p[2], ds[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int col = half * 32 + e + u;
+              bool vis;
+              float nl, dl;
+              if constexpr (kDKV) {
+                nl = meta->lse[col];
+                dl = meta->delta[col];
+                vis = !masked || (my_kt >= meta->kmin[col] && my_kt <= meta->kmax[col] &&
+                                  (!general || meta->doc[col] == my_doc));
+              } else {
+                nl = neg_lse;
+                dl = delta_i;
+                vis = (vis_w[half] >> (e + u)) & 1u;
+              }
+              const float pv = fast_exp2(fmaf(__uint_as_float(rs[e + u]), c, nl));
+              p[u] = vis ? pv : 0.f;
+              ds[u] = p[u] * (__uint_as_float(rd[e + u]) - dl) * scale;
+            }
+            pk_p[e / 2] = pack2<FP16>(p[0], p[1]);
+            pk_ds[e / 2] = pack2<FP16>(ds[0], ds[1]);
+          }
+          // K-major 128B-swizzled [128 x 64] tiles: 16-byte chunk ch of row r sits at
+          // r * 128 + ((ch ^ (r & 7)) << 4)
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int ch = half * 4 + q4;
+            const uint32_t off = row * 128 + ((ch ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDS + off), "r"(pk_ds[q4 * 4]),
+                         "r"(pk_ds[q4 * 4 + 1]), "r"(pk_ds[q4 * 4 + 2]), "r"(pk_ds[q4 * 4 + 3])
+                         : "memory");
+            if constexpr (kDKV) {
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off), "r"(pk_p[q4 * 4]),
+                           "r"(pk_p[q4 * 4 + 1]), "r"(pk_p[q4 * 4 + 2]), "r"(pk_p[q4 * 4 + 3])
+                           : "memory");
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bar_p_full);
+      }
+
+      // ---------------------------------------------------------------- epilogue
+      if (ok) ok = mbar_wait(bar_acc_done, (n_tiles - 1) & 1, abort_flag, prm.status);
+      if (ok) {
+        tc_fence_after();
+        const size_t row_off = ((size_t)bh * prm.N + (size_t)my_row) * D * 2;
+#pragma unroll
+        for (int a = 0; a < (kDKV ? 2 : 1); ++a) {
+          uint8_t* o_row = reinterpret_cast<uint8_t*>(a == 0 ? prm.out0 : prm.out1) + row_off;
+#pragma unroll
+          for (int q4 = 0; q4 < D / 32; ++q4) {
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_addr + (a == 0 ? Cfg::kColAcc0 : Cfg::kColAcc1) + q4 * 32, r);
+            tmem_wait_ld();
+            if (my_valid) {
+#pragma unroll
+              for (int e = 0; e < 32; e += 8) {
+                uint4 u;
+                u.x = pack2<FP16>(__uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+                u.y = pack2<FP16>(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+                u.z = pack2<FP16>(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
+                u.w = pack2<FP16>(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
+                *reinterpret_cast<uint4*>(o_row + q4 * 64 + e * 2) = u;
+              }
+            }
+          }
+        }
+        tc_fence_before();
+      }
+    }
+  } else if (!bail && warp < 4) {
+    // nothing streams through this tile: its gradients are zero
+    const int my_row = kDKV ? ks * (x0 + tid) + stream : x0 + tid;
+    const bool my_valid = kDKV ? (x0 + tid < Tk) : (my_row < prm.N);
+    if (my_valid) {
+      const size_t row_off = ((size_t)bh * prm.N + (size_t)my_row) * D * 2;
+      for (int a = 0; a < (kDKV ? 2 : 1); ++a) {
+        uint4* o_row = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a == 0 ? prm.out0 : prm.out1) + row_off);
+        for (int e = 0; e < D / 8; ++e) o_row[e] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+
+  // the stationary tiles were requested before the plan was known: never leave with them in flight
+  if (warp == 4 && lane == 0) mbar_wait(bar_x_full, 0, abort_flag, prm.status);
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc<Cfg::kTmemCols>(tmem);
+  }
+}
+
+}  // namespace spsattn

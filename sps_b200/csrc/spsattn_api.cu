@@ -17,6 +17,7 @@
 #include "model_glue.cuh"
 #include "prefill_aux.cuh"
 #include "prefill_sm100.cuh"
+#include "prefill_bwd_sm100.cuh"
 #include "rope.cuh"
 
 using namespace spsattn;
@@ -71,13 +72,14 @@ struct Strides {
   int64_t b, h, n;
 };
 
-// Q map: [D, N, H, B] with the operand's own strides, box [64, 128, 1, 1]
-int encode_q_map(CUtensorMap* tm, const void* ptr, int B, int H, int N, int D, Strides st, int dtype) {
+// Q map: [D, N, H, B] with the operand's own strides, box [64, box_rows, 1, 1]
+int encode_q_map(CUtensorMap* tm, const void* ptr, int B, int H, int N, int D, Strides st, int dtype,
+                 int box_rows = 128) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return SPSATTN_ERR_DRIVER;
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)st.n * 2, (cuuint64_t)st.h * 2, (cuuint64_t)st.b * 2};
-  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(tm, dtype == SPSATTN_DTYPE_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
@@ -126,6 +128,23 @@ int launch_prefill_sm100(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   const long long blocks = (long long)prm.n_qtiles * prm.B * prm.H;
   if (blocks <= 0 || blocks > 0x7fffffffLL) return SPSATTN_ERR_TOO_LARGE;
   prefill_sm100_kernel<D, FP16><<<(unsigned)blocks, kPrefillThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, prm);
+  return (int)cudaGetLastError();
+}
+
+template <int D, bool FP16, int MODE>
+int launch_prefill_bwd(const CUtensorMap& x0, const CUtensorMap& x1, const CUtensorMap& y0,
+                       const CUtensorMap& y1, const BwdParams& prm, cudaStream_t st) {
+  using Cfg = BwdCfg<D>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(prefill_bwd_sm100_kernel<D, FP16, MODE>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return (int)attr_err;
+  const long long blocks = (long long)prm.n_xtiles * prm.B * prm.H;
+  if (blocks <= 0 || blocks > 0x7fffffffLL) return SPSATTN_ERR_TOO_LARGE;
+  prefill_bwd_sm100_kernel<D, FP16, MODE><<<(unsigned)blocks, kBwdThreads, Cfg::kSmemBytes, st>>>(x0, x1, y0, y1, prm);
   return (int)cudaGetLastError();
 }
 
@@ -395,6 +414,99 @@ int spsattn_prefill_fwd_strided(const void* q, const void* k, const void* v, voi
     prefill_generic_kernel<false><<<grid, 128, smem, st>>>(q, k, v, o, lse, doc_ids, doc_is_i64, doc_stride_b,
                                                            doc_stride_t, lo, mono, H, N, D, mask, scale_log2);
   return (int)cudaGetLastError();
+}
+
+size_t spsattn_prefill_bwd_workspace_bytes(int B, int H, int N, int D) {
+  if (B <= 0 || H <= 0 || N <= 0) return 256;
+  return spsattn_prefill_workspace_bytes(B, H, N, D) + align_up((size_t)B * H * N * sizeof(float), 256);
+}
+
+int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                        const float* lse, void* dq, void* dk, void* dv, const void* doc_ids,
+                        int doc_is_i64, int64_t doc_stride_b, int64_t doc_stride_t, int B, int H, int N,
+                        int D, int dtype, float sm_scale, int persistent_parity, int temporary_window,
+                        int persistent_window, int mask_flags, void* workspace, size_t workspace_bytes,
+                        int* device_status, void* stream) {
+  if (!q || !k || !v || !o || !d_o || !lse || !dq || !dk || !dv) return SPSATTN_ERR_ARG;
+  if (B <= 0 || H <= 0 || N <= 0) return SPSATTN_ERR_ARG;
+  if (dtype != SPSATTN_DTYPE_BF16 && dtype != SPSATTN_DTYPE_FP16) return SPSATTN_ERR_ARG;
+  if (persistent_parity != SPSATTN_PARITY_EVEN && persistent_parity != SPSATTN_PARITY_ODD &&
+      persistent_parity != SPSATTN_PARITY_NONE)
+    return SPSATTN_ERR_ARG;
+  if (!(sm_scale > 0.f) || !isfinite(sm_scale)) return SPSATTN_ERR_ARG;
+  if (D != 64 && D != 128) return SPSATTN_ERR_HEAD_DIM;
+  if (persistent_parity != SPSATTN_PARITY_NONE && (N & 1)) return SPSATTN_ERR_ODD_LENGTH;
+  if (N > 64 * kBwdTable) return SPSATTN_ERR_TOO_LARGE;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o) ||
+      !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
+    return SPSATTN_ERR_ALIGN;
+  if ((long long)B * H > 0x7fffffffLL / 1024) return SPSATTN_ERR_TOO_LARGE;
+  if (workspace == nullptr || workspace_bytes < spsattn_prefill_bwd_workspace_bytes(B, H, N, D))
+    return SPSATTN_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return SPSATTN_ERR_ALIGN;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool fp16 = dtype == SPSATTN_DTYPE_FP16;
+
+  int *lo = nullptr, *mono = nullptr;
+  const size_t pre_bytes = spsattn_prefill_workspace_bytes(B, H, N, D);
+  int rc = run_doc_prepass(doc_ids, doc_is_i64, doc_stride_b, doc_stride_t, B, N, workspace, pre_bytes,
+                           &lo, &mono, st);
+  if (rc != 0) return rc;
+  float* delta = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + pre_bytes);
+  const long long rows = (long long)B * H * N;
+  const unsigned dgrid = (unsigned)((rows + 7) / 8);
+  if (fp16) bwd_delta_kernel<true><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows, D);
+  else bwd_delta_kernel<false><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows, D);
+  if ((rc = (int)cudaGetLastError()) != 0) return rc;
+
+  const MaskParams mask = make_mask(N, persistent_parity, temporary_window, persistent_window, mask_flags);
+  const Strides dense = {(int64_t)H * N * D, (int64_t)N * D, (int64_t)D};
+  CUtensorMap q128, do128, q64, do64, ks_map, vs_map;
+  if ((rc = encode_q_map(&q128, q, B, H, N, D, dense, dtype, 128)) != 0) return rc;
+  if ((rc = encode_q_map(&do128, d_o, B, H, N, D, dense, dtype, 128)) != 0) return rc;
+  if ((rc = encode_q_map(&q64, q, B, H, N, D, dense, dtype, 64)) != 0) return rc;
+  if ((rc = encode_q_map(&do64, d_o, B, H, N, D, dense, dtype, 64)) != 0) return rc;
+  if ((rc = encode_kv_map(&ks_map, k, B, H, N, D, mask.ks, dense, dtype)) != 0) return rc;
+  if ((rc = encode_kv_map(&vs_map, v, B, H, N, D, mask.ks, dense, dtype)) != 0) return rc;
+
+  BwdParams prm;
+  memset(&prm, 0, sizeof(prm));
+  prm.lse = lse;
+  prm.delta = delta;
+  prm.docs = doc_ids;
+  prm.doc_stride_b = doc_stride_b;
+  prm.doc_stride_t = doc_stride_t;
+  prm.doc_is_i64 = doc_is_i64;
+  prm.lo = lo;
+  prm.mono = mono;
+  prm.B = B;
+  prm.H = H;
+  prm.N = N;
+  prm.mask = mask;
+  prm.scale_log2 = sm_scale * 1.4426950408889634f;
+  prm.sm_scale = sm_scale;
+  prm.status = device_status;
+
+  // dK, dV: one block per 128-token key tile of each parity stream
+  prm.out0 = dk;
+  prm.out1 = dv;
+  prm.n_xtiles = mask.ks * ((N / mask.ks + 127) / 128);
+  if (D == 64)
+    rc = fp16 ? launch_prefill_bwd<64, true, kBwdDKV>(ks_map, vs_map, q64, do64, prm, st)
+              : launch_prefill_bwd<64, false, kBwdDKV>(ks_map, vs_map, q64, do64, prm, st);
+  else
+    rc = fp16 ? launch_prefill_bwd<128, true, kBwdDKV>(ks_map, vs_map, q64, do64, prm, st)
+              : launch_prefill_bwd<128, false, kBwdDKV>(ks_map, vs_map, q64, do64, prm, st);
+  if (rc != 0) return rc;
+  // dQ: one block per 128-row query tile
+  prm.out0 = dq;
+  prm.out1 = nullptr;
+  prm.n_xtiles = (N + 127) / 128;
+  if (D == 64)
+    return fp16 ? launch_prefill_bwd<64, true, kBwdDQ>(q128, do128, ks_map, vs_map, prm, st)
+                : launch_prefill_bwd<64, false, kBwdDQ>(q128, do128, ks_map, vs_map, prm, st);
+  return fp16 ? launch_prefill_bwd<128, true, kBwdDQ>(q128, do128, ks_map, vs_map, prm, st)
+              : launch_prefill_bwd<128, false, kBwdDQ>(q128, do128, ks_map, vs_map, prm, st);
 }
 
 int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, float* lse,

@@ -1,4 +1,5 @@
-"""Generate tests/golden/reference_vectors.npz from the reference's own CPU oracles.
+"""Generate tests/golden/reference_vectors.npz and reference_grad_vectors.npz (``--grads-only``
+writes just the second) from the reference's own CPU oracles.
 
 Run once, in a container that has the reference checkout (it cannot travel to
 the GPU box, so the vectors are committed):
@@ -55,13 +56,18 @@ from modeling.tests.models.attention.test_segmented_q2_attention import _referen
 OUT = {}
 
 
-def put(name, t):
+def put(name, t, half=False):
     """Store one array; floats that are exactly bf16-representable are stored as
-    their 16-bit patterns under ``<name>__bf16`` (tests/golden/loader.py widens them)."""
+    their 16-bit patterns under ``<name>__bf16`` (tests/golden/loader.py widens them);
+    ``half`` stores a float tensor rounded to fp16 under ``<name>__f16`` (gradients, which are
+    compared at 4e-2)."""
     if isinstance(t, torch.Tensor):
         t = t.detach().cpu()
         if t.is_floating_point():
             t = t.float()
+            if half:
+                OUT[name + "__f16"] = t.half().numpy()
+                return
             if t.numel() > 64 and torch.equal(t.bfloat16().float(), t):
                 OUT[name + "__bf16"] = t.bfloat16().view(torch.int16).numpy().view(np.uint16)
                 return
@@ -409,7 +415,63 @@ def standard_model_cases():
     put("model_std_eos_end_greedy", model.generate(ends, 5, do_sample=False, stop_on_eos=False))
 
 
+def grad_cases():
+    """dQ, dK, dV by autograd through the reference's own SDPA oracles, the way its backward tests
+    obtain them (test_sps_attention.py:79-131, test_full_flash_attention.py:126-160)."""
+    def grads(fn, q, k, v, g):
+        qs = [t.clone().requires_grad_(True) for t in (q, k, v)]
+        with torch.enable_grad():
+            fn(*qs).backward(g)
+        return [t.grad for t in qs]
+
+    # the reference's own backward case and larger packed ones
+    for tag, (b, h, n, d, w, mean, seed) in {
+        "t16_nodoc": (1, 2, 32, 64, 3, 0, 17), "t16_doc": (1, 2, 32, 64, 3, -1, 17),
+        "n200": (2, 2, 200, 64, 7, 30, 3), "n384": (1, 2, 384, 64, 64, 60, 4),
+        "n256_d128": (1, 2, 256, 128, 16, 50, 5),
+    }.items():
+        gen = torch.Generator().manual_seed(1000 + seed + n)
+        q, k, v, g = (torch.randn(b, h, n, d, generator=gen).bfloat16().float() for _ in range(4))
+        docs = None
+        if mean == -1:
+            docs = torch.tensor([[0] * 6 + [1] * 8 + [2] * 2]).repeat_interleave(2, dim=1)
+        elif mean > 0:
+            docs = geometric_docs(b, n // 2, mean, seed)
+        dq, dk, dv = grads(lambda a, b_, c: _sdpa_reference_attention_sps(a, b_, c, w, documents_idx_BxT=docs),
+                           q, k, v, g)
+        name = f"grad_sps_{tag}"
+        put(f"{name}_q", q), put(f"{name}_k", k), put(f"{name}_v", v), put(f"{name}_do", g)
+        put(f"{name}_w", np.int64(w))
+        if docs is not None:
+            put(f"{name}_docs", docs)
+        put(f"{name}_dq", dq, True), put(f"{name}_dk", dk, True), put(f"{name}_dv", dv, True)
+    # Standard model: causal + same document
+    gen = torch.Generator().manual_seed(2024)
+    q, k, v, g = (torch.randn(2, 2, 200, 64, generator=gen).bfloat16().float() for _ in range(4))
+    docs = geometric_docs(2, 200, 40, 6)[:, ::2].contiguous()
+    dq, dk, dv = grads(lambda a, b_, c: _pytorch_reference_attention(a, b_, c, 0.125, docs), q, k, v, g)
+    put("grad_full_q", q), put("grad_full_k", k), put("grad_full_v", v), put("grad_full_do", g)
+    put("grad_full_docs", docs), put("grad_full_dq", dq, True), put("grad_full_dk", dk, True), put("grad_full_dv", dv, True)
+    # persistent window, both parities
+    for rem in (0, 1):
+        gen = torch.Generator().manual_seed(70 + rem)
+        q, k, v, g = (torch.randn(1, 2, 96, 64, generator=gen).bfloat16().float() for _ in range(4))
+        dq, dk, dv = grads(lambda a, b_, c: _reference_persistent_key_window_attention(
+            a, b_, c, persistent_key_window=5, persistent_key_remainder=rem, temporary_key_window=2), q, k, v, g)
+        name = f"grad_pkw{rem}"
+        put(f"{name}_q", q), put(f"{name}_k", k), put(f"{name}_v", v), put(f"{name}_do", g)
+        put(f"{name}_dq", dq, True), put(f"{name}_dk", dk, True), put(f"{name}_dv", dv, True)
+
+
 if __name__ == "__main__":
+    here = os.path.dirname(os.path.abspath(__file__))
+    grad_cases()
+    gpath = os.path.join(here, "reference_grad_vectors.npz")
+    np.savez_compressed(gpath, **OUT)
+    print(f"wrote {gpath}: {len(OUT)} arrays, {os.path.getsize(gpath) / 1e6:.2f} MB")
+    OUT.clear()
+    if "--grads-only" in sys.argv:
+        raise SystemExit(0)
     with torch.no_grad():
         sps_cases()
         persistent_window_cases()
