@@ -263,6 +263,36 @@ def run_ours(args):
         }
         del hq, hk, hv, ho, dev_in, dev_out
 
+    # ---------------- backward of the same prefill (training path): dQ, dK, dV from dO
+    if not args.skip_backward:
+        o_b, lse_b = sps_b200.prefill_attention(wl.q, wl.k, wl.v, wl.sm_scale, persistent_parity=0,
+                                                temporary_window=wl.window, documents_idx=wl.docs,
+                                                return_lse=True)
+        d_o = torch.randn(wl.q.shape, device=device, dtype=torch.float32).to(wl.q.dtype)
+
+        def backward_step():
+            sps_b200.attention.prefill_attention_backward(
+                wl.q, wl.k, wl.v, o_b, lse_b, d_o, wl.sm_scale, persistent_parity=0,
+                temporary_window=wl.window, documents_idx=wl.docs)
+
+        kb = max(3, min(K, 30))
+        b_region, b_launch = timed_steps(backward_step, kb, 3, world, device)
+        # five products per visible (query, key) pair against the forward's two
+        b_flops = 2.5 * wl.flops
+        tb = b_flops / (b_launch * 1e-3) / 1e12
+        result["prefill_backward"] = {
+            "workload": f"{PREFILL}: dQ, dK, dV of the same batch from dO (delta pre-pass + dK/dV kernel + "
+                        "dQ kernel per step), per GPU",
+            "useful_gflop_per_step_per_gpu": b_flops / 1e9, "ms_per_step": b_region / kb,
+            "useful_tflops": world * b_flops * kb / (b_region * 1e-3) / 1e12, "gpu_launches": 4 * kb,
+            "roofline": {"bound": "tensor", "achieved": tb, "peak": peak, "unit": "TFLOP/s", "frac": tb / peak,
+                         "traffic": None, "peak_source": f"{peak_kind} bf16 burst", "launch_ms": b_launch,
+                         "note": "useful FLOPs = 2.5 x forward; the two kernels recompute S and dP, so they "
+                                 "execute 3.5 x forward"},
+        }
+        del o_b, lse_b, d_o
+        sps_b200.check_device_status(device)
+
     # ---------------- the least sparse prefill mask: head_dim 128, window = whole document
     if not args.skip_full_window:
         del wl, out
@@ -530,6 +560,7 @@ def main():
     ap.add_argument("--case", choices=["full", "prefill-small", "decode-small", "generation-small", "generation"], default="full")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--skip-backward", action="store_true", help="skip the prefill backward section")
     ap.add_argument("--skip-full-window", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-generation", action="store_true")

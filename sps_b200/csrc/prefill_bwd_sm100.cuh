@@ -90,7 +90,7 @@ bwd_delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float
   if (lane == 0) delta[r] = acc;
 }
 
-struct BwdMeta {           // per streamed query tile in kDKV mode: one entry per column
+struct alignas(16) BwdMeta {   // per streamed query tile in kDKV mode: one entry per column
   float lse[64];
   float delta[64];
   int kmin[64];
@@ -424,6 +424,41 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
       const int my_kt = x0 + row;                     // kDKV: this thread's key token
       bool ok = true;
 
+      // kDKV: the per-column constants of a streamed query tile (lse, delta, visible key interval,
+      // document id) are fetched one tile ahead by the first 64 threads: the loads are issued
+      // when tile j starts and land in shared memory when it ends
+      float pf_l = 0.f, pf_dl = 0.f;
+      int pf_lo = 0;
+      long long pf_doc = 0;
+      auto meta_fetch = [&](int jj) {
+        const int i = (s_tiles[jj] >> 1) * 64 + tid;
+        pf_l = 0.f, pf_dl = 0.f, pf_lo = 0, pf_doc = 0;
+        if (i < prm.N) {
+          pf_l = prm.lse[(size_t)bh * prm.N + i];
+          pf_dl = prm.delta[(size_t)bh * prm.N + i];
+          if (lo_b != nullptr) pf_lo = lo_b[i];
+          if (general) pf_doc = doc_at(i);
+        }
+      };
+      auto meta_publish = [&](int jj) {
+        const int i = (s_tiles[jj] >> 1) * 64 + tid;
+        BwdMeta* mw = &s_meta[jj & 1];
+        int kmin = 0, kmax = -1;
+        if (i < prm.N) row_interval(prm.mask, i, pf_lo, stream, kmin, kmax);
+        mw->lse[tid] = -pf_l;
+        mw->delta[tid] = pf_dl;
+        mw->kmin[tid] = kmin;
+        mw->kmax[tid] = kmax;
+        mw->doc[tid] = pf_doc;
+        mbar_arrive(bar_meta + 8 * (jj & 1));
+      };
+      if constexpr (kDKV) {
+        if (tid < 64) {
+          meta_fetch(0);
+          meta_publish(0);
+        }
+      }
+
       for (int j = 0; j < n_tiles; ++j) {
         bool masked;
         int y_first = 0, y_stream = 0;                // kDQ: first key token and stream of the tile
@@ -431,27 +466,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         if constexpr (kDKV) {
           const int e = s_tiles[j];
           masked = (e & 1) != 0;
-          const int q0 = (e >> 1) * 64;
-          BwdMeta* mw = &s_meta[j & 1];
-          meta = mw;
-          if (tid < 64) {
-            const int i = q0 + tid;
-            float l = 0.f, dl = 0.f;
-            int kmin = 0, kmax = -1;
-            long long dd = 0;
-            if (i < prm.N) {
-              l = prm.lse[(size_t)bh * prm.N + i];
-              dl = prm.delta[(size_t)bh * prm.N + i];
-              row_interval(prm.mask, i, lo_b != nullptr ? lo_b[i] : 0, stream, kmin, kmax);
-              if (general) dd = doc_at(i);
-            }
-            mw->lse[tid] = -l;
-            mw->delta[tid] = dl;
-            mw->kmin[tid] = kmin;
-            mw->kmax[tid] = kmax;
-            mw->doc[tid] = dd;
-            mbar_arrive(bar_meta + 8 * (j & 1));
-          }
+          meta = &s_meta[j & 1];
           if (!mbar_wait(bar_meta + 8 * (j & 1), (j >> 1) & 1, abort_flag, prm.status)) {
             ok = false;
             break;
@@ -473,6 +488,10 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           }
         }
         tc_fence_after();
+        if constexpr (kDKV) {
+          // every thread is past tile j-1 here, so the other meta buffer may be refilled
+          if (tid < 64 && j + 1 < n_tiles) meta_fetch(j + 1);
+        }
 
         // kDQ: the visible keys of this row form an interval of the tile's 64 columns
         uint32_t vis_w[2] = {0xffffffffu, 0xffffffffu};
@@ -498,37 +517,69 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           }
         }
 
+        if constexpr (kDKV) {
+          // visibility of the tile's 64 query columns for this thread's key, one bit each
+          if (masked) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t rs[32], rd[32];
-          tmem_ld32(tmem + lane_addr + Cfg::kColS + half * 32, rs);
-          tmem_ld32(tmem + lane_addr + Cfg::kColDP + half * 32, rd);
+            for (int q4 = 0; q4 < 2; ++q4) {
+              uint32_t bits = 0;
+#pragma unroll
+              for (int e = 0; e < 32; e += 4) {
+                const int4 lo4 = *reinterpret_cast<const int4*>(&meta->kmin[q4 * 32 + e]);
+                const int4 hi4 = *reinterpret_cast<const int4*>(&meta->kmax[q4 * 32 + e]);
+                bits |= ((my_kt >= lo4.x && my_kt <= hi4.x) ? 1u : 0u) << e;
+                bits |= ((my_kt >= lo4.y && my_kt <= hi4.y) ? 1u : 0u) << (e + 1);
+                bits |= ((my_kt >= lo4.z && my_kt <= hi4.z) ? 1u : 0u) << (e + 2);
+                bits |= ((my_kt >= lo4.w && my_kt <= hi4.w) ? 1u : 0u) << (e + 3);
+              }
+              if (general) {
+                for (int e = 0; e < 32; ++e)
+                  if (meta->doc[q4 * 32 + e] != my_doc) bits &= ~(1u << e);
+              }
+              vis_w[q4] = bits;
+            }
+          }
+        }
+
+        // columns are processed CH at a time; in kDKV mode the per-column constants of a chunk
+        // are staged in registers with vector loads before the scores arrive
+        constexpr int CH = kDKV ? 16 : 32;
+#pragma unroll
+        for (int chunk = 0; chunk < 64 / CH; ++chunk) {
+          float nl_c[kDKV ? CH : 1], dl_c[kDKV ? CH : 1];
+          if constexpr (kDKV) {
+#pragma unroll
+            for (int e = 0; e < CH; e += 4) {
+              const float4 a4 = *reinterpret_cast<const float4*>(&meta->lse[chunk * CH + e]);
+              const float4 b4 = *reinterpret_cast<const float4*>(&meta->delta[chunk * CH + e]);
+              nl_c[e] = a4.x, nl_c[e + 1] = a4.y, nl_c[e + 2] = a4.z, nl_c[e + 3] = a4.w;
+              dl_c[e] = b4.x, dl_c[e + 1] = b4.y, dl_c[e + 2] = b4.z, dl_c[e + 3] = b4.w;
+            }
+          }
+          uint32_t rs[CH], rd[CH];
+          if constexpr (CH == 32) {
+            tmem_ld32(tmem + lane_addr + Cfg::kColS + chunk * CH, rs);
+            tmem_ld32(tmem + lane_addr + Cfg::kColDP + chunk * CH, rd);
+          } else {
+            tmem_ld16(tmem + lane_addr + Cfg::kColS + chunk * CH, rs);
+            tmem_ld16(tmem + lane_addr + Cfg::kColDP + chunk * CH, rd);
+          }
           tmem_wait_ld();
-          if (half == 1) {
+          if (chunk == 64 / CH - 1) {
             tc_fence_before();
             mbar_arrive(bar_s_free);
           }
-          uint32_t pk_p[16], pk_ds[16];
+          const uint32_t vbits = vis_w[(chunk * CH) >> 5] >> ((chunk * CH) & 31);
+          uint32_t pk_p[CH / 2], pk_ds[CH / 2];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
+          for (int e = 0; e < CH; e += 2) {
             float p[2], ds[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-              const int col = half * 32 + e + u;
-              bool vis;
-              float nl, dl;
-              if constexpr (kDKV) {
-                nl = meta->lse[col];
-                dl = meta->delta[col];
-                vis = !masked || (my_kt >= meta->kmin[col] && my_kt <= meta->kmax[col] &&
-                                  (!general || meta->doc[col] == my_doc));
-              } else {
-                nl = neg_lse;
-                dl = delta_i;
-                vis = (vis_w[half] >> (e + u)) & 1u;
-              }
+              const float nl = kDKV ? nl_c[kDKV ? e + u : 0] : neg_lse;
+              const float dl = kDKV ? dl_c[kDKV ? e + u : 0] : delta_i;
               const float pv = fast_exp2(fmaf(__uint_as_float(rs[e + u]), c, nl));
-              p[u] = vis ? pv : 0.f;
+              p[u] = ((vbits >> (e + u)) & 1u) ? pv : 0.f;
               ds[u] = p[u] * (__uint_as_float(rd[e + u]) - dl) * scale;
             }
             pk_p[e / 2] = pack2<FP16>(p[0], p[1]);
@@ -537,8 +588,8 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           // K-major 128B-swizzled [128 x 64] tiles: 16-byte chunk ch of row r sits at
           // r * 128 + ((ch ^ (r & 7)) << 4)
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const int ch = half * 4 + q4;
+          for (int q4 = 0; q4 < CH / 8; ++q4) {
+            const int ch = chunk * (CH / 8) + q4;
             const uint32_t off = row * 128 + ((ch ^ (row & 7)) << 4);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDS + off), "r"(pk_ds[q4 * 4]),
                          "r"(pk_ds[q4 * 4 + 1]), "r"(pk_ds[q4 * 4 + 2]), "r"(pk_ds[q4 * 4 + 3])
@@ -553,6 +604,9 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(bar_p_full);
+        if constexpr (kDKV) {
+          if (tid < 64 && j + 1 < n_tiles) meta_publish(j + 1);
+        }
       }
 
       // ---------------------------------------------------------------- epilogue
