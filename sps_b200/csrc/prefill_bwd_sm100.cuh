@@ -63,31 +63,40 @@ struct BwdCfg {
   static constexpr int kOffDS = kOffP + kPBytes;
   static constexpr int kOffBar = kOffDS + kPBytes;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
-  static constexpr uint32_t kColS = 0, kColDP = 64, kColAcc0 = 128, kColAcc1 = 128 + D;
+  // S / dP accumulators: one pair at head_dim 64 (two blocks share the SM's 512 columns), two
+  // pairs at head_dim 128 (one block per SM: the next tile's products run under this tile's softmax)
+  static constexpr int kSBufs = (D == 64) ? 1 : 2;
+  static constexpr uint32_t kColS = 0, kColDP = 64, kSBufCols = 128;
+  static constexpr uint32_t kColAcc0 = kSBufs * kSBufCols, kColAcc1 = kColAcc0 + D;
   static constexpr uint32_t kTmemCols = (D == 64) ? 256 : 512;
   static constexpr int kBlocksPerSM = (D == 64) ? 2 : 1;
 };
 
-// delta[b, h, i] = sum_d dO * O: one warp per row of dense [B*H*N, D] operands
-template <bool FP16>
+// delta[b, h, i] = sum_d dO * O over dense [B*H*N, D] operands: D / 8 threads per row, 16 bytes
+// of each operand per thread
+template <bool FP16, int D>
 __global__ void __launch_bounds__(256)
 bwd_delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float* __restrict__ delta,
-                 long long rows, int D) {
-  const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (r >= rows) return;
-  const uint32_t* po = reinterpret_cast<const uint32_t*>(o) + r * (D / 2);
-  const uint32_t* pd = reinterpret_cast<const uint32_t*>(d_o) + r * (D / 2);
+                 long long rows) {
+  constexpr int TPR = D / 8;                  // threads per row (8 or 16)
+  const long long r = ((long long)blockIdx.x * 256 + threadIdx.x) / TPR;
+  const int part = threadIdx.x % TPR;
   float acc = 0.f;
-  for (int x = lane; x < D / 2; x += 32) {
-    float a0, a1, b0, b1;
-    unpack2<FP16>(po[x], a0, a1);
-    unpack2<FP16>(pd[x], b0, b1);
-    acc = fmaf(a0, b0, fmaf(a1, b1, acc));
+  if (r < rows) {
+    const uint4 a = reinterpret_cast<const uint4*>(o)[r * TPR + part];
+    const uint4 g = reinterpret_cast<const uint4*>(d_o)[r * TPR + part];
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      float a0, a1, b0, b1;
+      unpack2<FP16>(aw[x], a0, a1);
+      unpack2<FP16>(gw[x], b0, b1);
+      acc = fmaf(a0, b0, fmaf(a1, b1, acc));
+    }
   }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) delta[r] = acc;
+  for (int off = TPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (part == 0 && r < rows) delta[r] = acc;
 }
 
 struct alignas(16) BwdMeta {   // per streamed query tile in kDKV mode: one entry per column
@@ -139,11 +148,11 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
   const uint32_t bar_x_full = bar0;
   const uint32_t bar_y_full = bar0 + 8;      // [2]
   const uint32_t bar_y_empty = bar0 + 24;    // [2]
-  const uint32_t bar_s_full = bar0 + 40;
-  const uint32_t bar_s_free = bar0 + 48;
-  const uint32_t bar_p_full = bar0 + 56;
-  const uint32_t bar_acc_done = bar0 + 64;
-  const uint32_t bar_meta = bar0 + 72;       // [2]
+  const uint32_t bar_s_full = bar0 + 40;     // [2]
+  const uint32_t bar_s_free = bar0 + 56;     // [2]
+  const uint32_t bar_p_full = bar0 + 72;
+  const uint32_t bar_acc_done = bar0 + 80;
+  const uint32_t bar_meta = bar0 + 88;       // [2]
 
   const bool has_docs = prm.docs != nullptr;
   const bool general = has_docs && prm.mono != nullptr && prm.mono[b] == 0;
@@ -212,9 +221,9 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         mbar_init(bar_y_full + 8 * s, 1);
         mbar_init(bar_y_empty + 8 * s, 1);
         mbar_init(bar_meta + 8 * s, 64);
+        mbar_init(bar_s_full + 8 * s, 1);
+        mbar_init(bar_s_free + 8 * s, 128);
       }
-      mbar_init(bar_s_full, 1);
-      mbar_init(bar_s_free, 128);
       mbar_init(bar_p_full, 128);
       mbar_init(bar_acc_done, 1);
       fence_barrier_init();
@@ -331,10 +340,12 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
       auto issue_s = [&](int j) {
         const int st = j % Cfg::kStages;
         if (!warp_wait(bar_y_full + 8 * st, (j / Cfg::kStages) & 1, abort_flag, prm.status)) return false;
-        if (j >= 1) {
-          if (!warp_wait(bar_s_free, (j - 1) & 1, abort_flag, prm.status)) return false;
+        const int sb = j % Cfg::kSBufs;
+        if (j >= Cfg::kSBufs) {
+          if (!warp_wait(bar_s_free + 8 * sb, ((j / Cfg::kSBufs) - 1) & 1, abort_flag, prm.status)) return false;
         }
         tc_fence_after();
+        const uint32_t ts = tmem + sb * Cfg::kSBufCols;
         const uint32_t y0 = dyk_lo + ((st * 2 * Cfg::kYBytes) >> 4);
         const uint32_t y1 = y0 + (Cfg::kYBytes >> 4);
         if (elect_one()) {
@@ -342,17 +353,17 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t xa = ((kk / 4) * Cfg::kXSub + (kk % 4) * 32) >> 4;
             const uint32_t yb = ((kk / 4) * Cfg::kYSub + (kk % 4) * 32) >> 4;
-            if (kk == 0) umma_ss<false>(tmem + Cfg::kColS, dx0_lo + xa, dx_hi, y0 + yb, dyk_hi, idesc_s);
-            else umma_ss<true>(tmem + Cfg::kColS, dx0_lo + xa, dx_hi, y0 + yb, dyk_hi, idesc_s);
+            if (kk == 0) umma_ss<false>(ts + Cfg::kColS, dx0_lo + xa, dx_hi, y0 + yb, dyk_hi, idesc_s);
+            else umma_ss<true>(ts + Cfg::kColS, dx0_lo + xa, dx_hi, y0 + yb, dyk_hi, idesc_s);
           }
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t xa = ((kk / 4) * Cfg::kXSub + (kk % 4) * 32) >> 4;
             const uint32_t yb = ((kk / 4) * Cfg::kYSub + (kk % 4) * 32) >> 4;
-            if (kk == 0) umma_ss<false>(tmem + Cfg::kColDP, dx1_lo + xa, dx_hi, y1 + yb, dyk_hi, idesc_s);
-            else umma_ss<true>(tmem + Cfg::kColDP, dx1_lo + xa, dx_hi, y1 + yb, dyk_hi, idesc_s);
+            if (kk == 0) umma_ss<false>(ts + Cfg::kColDP, dx1_lo + xa, dx_hi, y1 + yb, dyk_hi, idesc_s);
+            else umma_ss<true>(ts + Cfg::kColDP, dx1_lo + xa, dx_hi, y1 + yb, dyk_hi, idesc_s);
           }
-          umma_commit(bar_s_full);
+          umma_commit(bar_s_full + 8 * sb);
         }
         __syncwarp();
         return true;
@@ -477,7 +488,9 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           y_first = t.k0;
           y_stream = t.stream;
         }
-        if (!mbar_wait(bar_s_full, j & 1, abort_flag, prm.status)) {
+        const int sb = j % Cfg::kSBufs;
+        const uint32_t ts = tmem + lane_addr + sb * Cfg::kSBufCols;
+        if (!mbar_wait(bar_s_full + 8 * sb, (j / Cfg::kSBufs) & 1, abort_flag, prm.status)) {
           ok = false;
           break;
         }
@@ -558,16 +571,16 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           }
           uint32_t rs[CH], rd[CH];
           if constexpr (CH == 32) {
-            tmem_ld32(tmem + lane_addr + Cfg::kColS + chunk * CH, rs);
-            tmem_ld32(tmem + lane_addr + Cfg::kColDP + chunk * CH, rd);
+            tmem_ld32(ts + Cfg::kColS + chunk * CH, rs);
+            tmem_ld32(ts + Cfg::kColDP + chunk * CH, rd);
           } else {
-            tmem_ld16(tmem + lane_addr + Cfg::kColS + chunk * CH, rs);
-            tmem_ld16(tmem + lane_addr + Cfg::kColDP + chunk * CH, rd);
+            tmem_ld16(ts + Cfg::kColS + chunk * CH, rs);
+            tmem_ld16(ts + Cfg::kColDP + chunk * CH, rd);
           }
           tmem_wait_ld();
           if (chunk == 64 / CH - 1) {
             tc_fence_before();
-            mbar_arrive(bar_s_free);
+            mbar_arrive(bar_s_free + 8 * sb);
           }
           const uint32_t vbits = vis_w[(chunk * CH) >> 5] >> ((chunk * CH) & 31);
           uint32_t pk_p[CH / 2], pk_ds[CH / 2];

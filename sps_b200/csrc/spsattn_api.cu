@@ -454,9 +454,14 @@ int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void*
   if (rc != 0) return rc;
   float* delta = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + pre_bytes);
   const long long rows = (long long)B * H * N;
-  const unsigned dgrid = (unsigned)((rows + 7) / 8);
-  if (fp16) bwd_delta_kernel<true><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows, D);
-  else bwd_delta_kernel<false><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows, D);
+  const unsigned dgrid = (unsigned)((rows * (D / 8) + 255) / 256);
+  if (D == 64) {
+    if (fp16) bwd_delta_kernel<true, 64><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows);
+    else bwd_delta_kernel<false, 64><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows);
+  } else {
+    if (fp16) bwd_delta_kernel<true, 128><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows);
+    else bwd_delta_kernel<false, 128><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows);
+  }
   if ((rc = (int)cudaGetLastError()) != 0) return rc;
 
   const MaskParams mask = make_mask(N, persistent_parity, temporary_window, persistent_window, mask_flags);
