@@ -441,7 +441,7 @@ def run_generation(name, world, rank, device, peaks, peak_kind, new_tokens=None,
 def run_case(args):
     """Small single-kernel cases for profiler captures (a few hundred MB on the device, inputs
     still larger than L2): `prefill-small` = 4 of the 8 batch rows of the s-scale prefill,
-    `decode-small` = 32 of the 128 decode sequences, `generation-small` / `generation` = the
+    `backward-small` = the backward of those 4 rows, `decode-small` = 32 of the 128 decode sequences, `generation-small` / `generation` = the
     whole-model generation leg alone on a tiny / the full model.  Prints a short JSON line, not
     the benchmark contract line."""
     import sps_b200
@@ -460,6 +460,16 @@ def run_case(args):
         fn = lambda: sps_b200.prefill_attention(wl.q, wl.k, wl.v, wl.sm_scale, persistent_parity=0,
                                                 temporary_window=wl.window, documents_idx=wl.docs, out=out)
         work, unit = wl.flops / 1e12, "TFLOP/s"
+    elif args.case == "backward-small":
+        wl = workloads.make_prefill(PREFILL, device, batch_slice=slice(0, 4))
+        o_b, lse_b = sps_b200.prefill_attention(wl.q, wl.k, wl.v, wl.sm_scale, persistent_parity=0,
+                                                temporary_window=wl.window, documents_idx=wl.docs,
+                                                return_lse=True)
+        d_o = torch.randn(wl.q.shape, device=device, dtype=torch.float32).to(wl.q.dtype)
+        fn = lambda: sps_b200.attention.prefill_attention_backward(
+            wl.q, wl.k, wl.v, o_b, lse_b, d_o, wl.sm_scale, persistent_parity=0,
+            temporary_window=wl.window, documents_idx=wl.docs)
+        work, unit = 2.5 * wl.flops / 1e12, "TFLOP/s"
     else:
         dw = workloads.make_decode(DECODE, device, seq_slice=slice(0, 32))
         segs = [sps_b200.KVSegment(dw.ring_k, dw.ring_v, dw.ring_len, max_len_cap=dw.ring_k.shape[2]),
@@ -557,7 +567,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--case", choices=["full", "prefill-small", "decode-small", "generation-small", "generation"], default="full")
+    ap.add_argument("--case", choices=["full", "prefill-small", "backward-small", "decode-small", "generation-small", "generation"], default="full")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-decode", action="store_true")
     ap.add_argument("--skip-backward", action="store_true", help="skip the prefill backward section")
