@@ -250,9 +250,9 @@ def test_argument_errors():
     q = torch.randn(1, 1, 8, 48, device=_dev()).bfloat16()
     with pytest.raises(AssertionError):
         sps_b200.sps_sliding_attention(q, q, q, 0.125, 2)           # head_dim
-    q = torch.randn(1, 1, 8, 64, device=_dev()).bfloat16().requires_grad_(True)
+    q = torch.randn(1, 1, 8, 32, device=_dev()).bfloat16().requires_grad_(True)
     with pytest.raises(RuntimeError):
-        sps_b200.sps_sliding_attention(q, q, q, 0.125, 2)           # forward only
+        sps_b200.sps_sliding_attention(q, q, q, 0.125, 2)           # head_dim 32 is forward only
     with pytest.raises(RuntimeError):
         sps_b200.sps_sliding_attention(q.detach().cpu(), q.detach().cpu(), q.detach().cpu(), 0.125, 2)
 
