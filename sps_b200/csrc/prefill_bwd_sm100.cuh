@@ -100,8 +100,8 @@ bwd_delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float
 }
 
 struct alignas(16) BwdMeta {   // per streamed query tile in kDKV mode: one entry per column
-  float lse[64];
-  float delta[64];
+  float lse[64];     // -lse (log2 domain)
+  float delta[64];   // -delta * sm_scale
   int kmin[64];
   int kmax[64];
   long long doc[64];
@@ -425,7 +425,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
       if constexpr (!kDKV) {
         if (my_valid) {
           neg_lse = -prm.lse[(size_t)bh * prm.N + my_row];
-          delta_i = prm.delta[(size_t)bh * prm.N + my_row];
+          delta_i = -prm.delta[(size_t)bh * prm.N + my_row] * prm.sm_scale;   // enters as an FMA addend
         }
         const int lo_i = (lo_b != nullptr && my_valid) ? lo_b[my_row] : 0;
         row_interval(prm.mask, my_row, lo_i, 0, kmin_s[0], kmax_s[0]);
@@ -457,7 +457,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         int kmin = 0, kmax = -1;
         if (i < prm.N) row_interval(prm.mask, i, pf_lo, stream, kmin, kmax);
         mw->lse[tid] = -pf_l;
-        mw->delta[tid] = pf_dl;
+        mw->delta[tid] = -pf_dl * prm.sm_scale;
         mw->kmin[tid] = kmin;
         mw->kmax[tid] = kmax;
         mw->doc[tid] = pf_doc;
@@ -584,19 +584,22 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           }
           const uint32_t vbits = vis_w[(chunk * CH) >> 5] >> ((chunk * CH) & 31);
           uint32_t pk_p[CH / 2], pk_ds[CH / 2];
+          // packed fp32x2 arithmetic: one FFMA2 forms two exponents, one FFMA2 + one FMUL2 two dS
+          const float2 c2 = make_float2(c, c), sc2 = make_float2(scale, scale);
 #pragma unroll
           for (int e = 0; e < CH; e += 2) {
-            float p[2], ds[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const float nl = kDKV ? nl_c[kDKV ? e + u : 0] : neg_lse;
-              const float dl = kDKV ? dl_c[kDKV ? e + u : 0] : delta_i;
-              const float pv = fast_exp2(fmaf(__uint_as_float(rs[e + u]), c, nl));
-              p[u] = ((vbits >> (e + u)) & 1u) ? pv : 0.f;
-              ds[u] = p[u] * (__uint_as_float(rd[e + u]) - dl) * scale;
-            }
-            pk_p[e / 2] = pack2<FP16>(p[0], p[1]);
-            pk_ds[e / 2] = pack2<FP16>(ds[0], ds[1]);
+            const float2 nl2 = kDKV ? make_float2(nl_c[kDKV ? e : 0], nl_c[kDKV ? e + 1 : 0])
+                                    : make_float2(neg_lse, neg_lse);
+            const float2 nd2 = kDKV ? make_float2(dl_c[kDKV ? e : 0], dl_c[kDKV ? e + 1 : 0])
+                                    : make_float2(delta_i, delta_i);      // -delta * scale
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), c2, nl2);
+            float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            p.x = ((vbits >> e) & 1u) ? p.x : 0.f;
+            p.y = ((vbits >> (e + 1)) & 1u) ? p.y : 0.f;
+            const float2 t = __ffma2_rn(make_float2(__uint_as_float(rd[e]), __uint_as_float(rd[e + 1])), sc2, nd2);
+            const float2 ds = __fmul2_rn(p, t);
+            pk_p[e / 2] = pack2<FP16>(p.x, p.y);
+            pk_ds[e / 2] = pack2<FP16>(ds.x, ds.y);
           }
           // K-major 128B-swizzled [128 x 64] tiles: 16-byte chunk ch of row r sits at
           // r * 128 + ((ch ^ (r & 7)) << 4)
