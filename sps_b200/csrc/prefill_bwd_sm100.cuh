@@ -39,6 +39,7 @@ struct BwdParams {
   int64_t doc_stride_b, doc_stride_t;
   int doc_is_i64;
   const int* lo;
+  const int* hi;         // [B, N] last row of the run of equal ids containing the row (with lo)
   const int* mono;
   int B, H, N;
   int n_xtiles;          // stationary tiles per (batch, head)
@@ -97,6 +98,23 @@ bwd_delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float
 #pragma unroll
   for (int off = TPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (part == 0 && r < rows) delta[r] = acc;
+}
+
+// hi[b][i] = last row of the run of equal document ids that contains row i, from the run starts
+// lo[b][.] of the document pre-pass (a non-decreasing step function): the first later row whose
+// run starts after i, minus one.
+__global__ void __launch_bounds__(256)
+bwd_run_end_kernel(const int* __restrict__ lo, int* __restrict__ hi, int N, long long total) {
+  const long long g = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (g >= total) return;
+  const int i = (int)(g % N);
+  const int* lo_b = lo + (g - i);
+  int a = i + 1, c = N;
+  while (a < c) {
+    const int mid = (a + c) >> 1;
+    if (lo_b[mid] > i) c = mid; else a = mid + 1;
+  }
+  hi[g] = a - 1;
 }
 
 struct alignas(16) BwdMeta {   // per streamed query tile in kDKV mode: one entry per column
@@ -199,15 +217,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           i_hi = min(i_hi, 2ll * (kl + max(prm.mask.w, 0)) + 1);
         }
       }
-      if (lo_b != nullptr) {
-        // first row after jr_last that starts a later run (lo is a non-decreasing step function)
-        int a = jr_last + 1, c = prm.N;
-        while (a < c) {
-          const int mid = (a + c) >> 1;
-          if (lo_b[mid] > jr_last) c = mid; else a = mid + 1;
-        }
-        i_hi = min(i_hi, (long long)a - 1);
-      }
+      if (lo_b != nullptr) i_hi = min(i_hi, (long long)prm.hi[(size_t)b * prm.N + jr_last]);
       int first = jr_first / 64, n = 0;
       if (x0 < Tk && i_hi >= jr_first) n = min((int)(i_hi / 64) - first + 1, kBwdTable);
       s_cand[0] = first;

@@ -418,7 +418,8 @@ int spsattn_prefill_fwd_strided(const void* q, const void* k, const void* v, voi
 
 size_t spsattn_prefill_bwd_workspace_bytes(int B, int H, int N, int D) {
   if (B <= 0 || H <= 0 || N <= 0) return 256;
-  return spsattn_prefill_workspace_bytes(B, H, N, D) + align_up((size_t)B * H * N * sizeof(float), 256);
+  return spsattn_prefill_workspace_bytes(B, H, N, D) + align_up((size_t)B * H * N * sizeof(float), 256) +
+         align_up((size_t)B * N * sizeof(int), 256);
 }
 
 int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
@@ -453,6 +454,12 @@ int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void*
                            &lo, &mono, st);
   if (rc != 0) return rc;
   float* delta = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + pre_bytes);
+  int* hi = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(delta) + align_up((size_t)B * H * N * sizeof(float), 256));
+  if (lo != nullptr) {
+    const long long total = (long long)B * N;
+    bwd_run_end_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(lo, hi, N, total);
+    if ((rc = (int)cudaGetLastError()) != 0) return rc;
+  }
   const long long rows = (long long)B * H * N;
   const unsigned dgrid = (unsigned)((rows * (D / 8) + 255) / 256);
   if (D == 64) {
@@ -483,6 +490,7 @@ int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void*
   prm.doc_stride_t = doc_stride_t;
   prm.doc_is_i64 = doc_is_i64;
   prm.lo = lo;
+  prm.hi = hi;
   prm.mono = mono;
   prm.B = B;
   prm.H = H;

@@ -119,6 +119,44 @@ def test_backward_matches_gradient_oracle(case):
     _close(got, ref, str(case))
 
 
+def test_backward_random_shapes_and_masks():
+    """Seeded random sweep: lengths that are no multiple of any tile, both parities and the Standard
+    rule, windows from 0 to the whole sequence, persistent windows, the skip flag, packed /
+    non-monotone / no documents, bf16 and fp16, head_dim 64 and 128."""
+    import sps_b200
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(7)
+    for case in range(40):
+        D = int(rng.choice([64, 128]))
+        parity = int(rng.choice([0, 1, -1]))
+        N = int(rng.integers(1, 500)) * 2 if parity >= 0 else int(rng.integers(1, 1000))
+        B, H = int(rng.integers(1, 3)), int(rng.integers(1, 3))
+        w = int(rng.choice([0, 1, 3, 17, 64, 200, N]))
+        pw = None if parity < 0 or rng.random() < 0.6 else int(rng.choice([-1, 0, 2, 40]))
+        flags = int(rng.random() < 0.2) if parity >= 0 else 0
+        kind = str(rng.choice(["none", "mono", "general"]))
+        T = N // 2 if parity >= 0 else N
+        docs = None
+        if kind == "mono":
+            docs = _packed_docs(B, T, int(rng.choice([3, 20, 150])), case)[:, ::2].contiguous()
+        elif kind == "general":
+            docs = torch.from_numpy(rng.integers(0, 3, (B, T)))
+        if docs is not None and parity >= 0:
+            docs = docs.repeat_interleave(2, dim=1)
+        dtype = torch.bfloat16 if rng.random() < 0.8 else torch.float16
+        gen = torch.Generator().manual_seed(case)
+        q, k, v, g = (torch.randn(B, H, N, D, generator=gen).to(dtype).float() for _ in range(4))
+        scale = 1.0 / math.sqrt(D)
+        _, got = _run(q, k, v, g, lambda a, b, c: sps_b200.prefill_attention(
+            a, b, c, scale, persistent_parity=parity, temporary_window=w, persistent_window=pw,
+            documents_idx=None if docs is None else docs.to(dev), mask_flags=flags), dtype)
+        ref = orc.prefill_attention_grads(q, k, v, g, scale, persistent_parity=parity, temporary_window=w,
+                                          persistent_window=pw, docs=docs, mask_flags=flags)
+        for x in got:
+            assert bool(torch.isfinite(x).all()), case
+        _close(got, ref, (case, D, parity, N, w, pw, flags, kind))
+
+
 def test_backward_is_linear_in_the_output_gradient():
     """At a multi-tile size: backward(a * g1 + g2) == a * backward(g1) + backward(g2) up to rounding."""
     import sps_b200
