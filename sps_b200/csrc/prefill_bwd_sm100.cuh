@@ -27,7 +27,7 @@ namespace spsattn {
 
 constexpr int kBwdDQ = 0;
 constexpr int kBwdDKV = 1;
-constexpr int kBwdThreads = 192;
+constexpr int kBwdMaxThreads = 320;
 constexpr int kBwdTable = 1024;      // streamed tiles listed per block (64K rows in kDKV mode)
 
 struct BwdParams {
@@ -61,12 +61,18 @@ struct BwdCfg {
   static constexpr int kOffX1 = kXBytes;
   static constexpr int kOffY = 2 * kXBytes;                    // [stage][Y0 | Y1]
   static constexpr int kOffP = kOffY + kStages * 2 * kYBytes;
-  static constexpr int kOffDS = kOffP + kPBytes;
-  static constexpr int kOffBar = kOffDS + kPBytes;
+  // softmax warpgroups per block: one at head_dim 64 (two blocks per SM), two at head_dim 128 (one
+  // block per SM), each with its own S / dP pair in TMEM and its own P / dS tiles, taking
+  // alternate streamed tiles
+  static constexpr int kWGs = (D == 64) ? 1 : 2;
+  static constexpr int kThreads = 32 * (4 * kWGs + 2);
+  static constexpr int kProducerWarp = 4 * kWGs, kMmaWarp = 4 * kWGs + 1;
+  static constexpr int kOffDS = kOffP + kPBytes;               // [warpgroup][P | dS]
+  static constexpr int kOffBar = kOffP + kWGs * 2 * kPBytes;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
   // S / dP accumulators: one pair at head_dim 64 (two blocks share the SM's 512 columns), two
   // pairs at head_dim 128 (one block per SM: the next tile's products run under this tile's softmax)
-  static constexpr int kSBufs = (D == 64) ? 1 : 2;
+  static constexpr int kSBufs = kWGs;
   static constexpr uint32_t kColS = 0, kColDP = 64, kSBufCols = 128;
   static constexpr uint32_t kColAcc0 = kSBufs * kSBufCols, kColAcc1 = kColAcc0 + D;
   static constexpr uint32_t kTmemCols = (D == 64) ? 256 : 512;
@@ -126,7 +132,7 @@ struct alignas(16) BwdMeta {   // per streamed query tile in kDKV mode: one entr
 };
 
 template <int D, bool FP16, int MODE>
-__global__ void __launch_bounds__(kBwdThreads, BwdCfg<D>::kBlocksPerSM)
+__global__ void __launch_bounds__(BwdCfg<D>::kThreads, BwdCfg<D>::kBlocksPerSM)
 prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__ CUtensorMap tm_x1,
                          const __grid_constant__ CUtensorMap tm_y0, const __grid_constant__ CUtensorMap tm_y1,
                          const BwdParams prm) {
@@ -137,7 +143,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
   __shared__ int s_tiles[kBwdTable];    // kDQ: packed key tiles; kDKV: (query tile << 1) | masked
   __shared__ int s_ntiles;
   __shared__ int s_cand[2];             // kDKV: first candidate query tile, number of candidates
-  __shared__ BwdMeta s_meta[kDKV ? 2 : 1];
+  __shared__ BwdMeta s_meta[kDKV ? 2 * BwdCfg<D>::kWGs : 1];   // [warpgroup][tile parity]
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
@@ -168,9 +174,9 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
   const uint32_t bar_y_empty = bar0 + 24;    // [2]
   const uint32_t bar_s_full = bar0 + 40;     // [2]
   const uint32_t bar_s_free = bar0 + 56;     // [2]
-  const uint32_t bar_p_full = bar0 + 72;
-  const uint32_t bar_acc_done = bar0 + 80;
-  const uint32_t bar_meta = bar0 + 88;       // [2]
+  const uint32_t bar_p_full = bar0 + 72;     // [warpgroup]
+  const uint32_t bar_acc_done = bar0 + 88;   // [warpgroup]
+  const uint32_t bar_meta = bar0 + 104;      // [warpgroup][2]
 
   const bool has_docs = prm.docs != nullptr;
   const bool general = has_docs && prm.mono != nullptr && prm.mono[b] == 0;
@@ -224,18 +230,19 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
       s_cand[1] = n;
     }
   }
-  if (warp == 4) {
+  if (warp == Cfg::kProducerWarp) {
     if (lane == 0) {
       mbar_init(bar_x_full, 1);
       for (int s = 0; s < 2; ++s) {
         mbar_init(bar_y_full + 8 * s, 1);
         mbar_init(bar_y_empty + 8 * s, 1);
         mbar_init(bar_meta + 8 * s, 64);
+        mbar_init(bar_meta + 16 + 8 * s, 64);
+        mbar_init(bar_p_full + 8 * s, 128);
+        mbar_init(bar_acc_done + 8 * s, 1);
         mbar_init(bar_s_full + 8 * s, 1);
         mbar_init(bar_s_free + 8 * s, 128);
       }
-      mbar_init(bar_p_full, 128);
-      mbar_init(bar_acc_done, 1);
       fence_barrier_init();
       tma_prefetch_desc(&tm_x0);
       tma_prefetch_desc(&tm_x1);
@@ -267,12 +274,12 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
 
   // ---- the list of streamed tiles
   if constexpr (!kDKV) {
-    for (int j = tid; j < min(s_plan.n_tiles, kBwdTable); j += kBwdThreads)
+    for (int j = tid; j < min(s_plan.n_tiles, kBwdTable); j += Cfg::kThreads)
       s_tiles[j] = pack_tile(tile_info(s_plan, j));
   } else {
     // per candidate query tile: does any row see any key of this tile, do all rows see all keys
     const int first = s_cand[0], n_cand = s_cand[1];
-    for (int cnd = warp; cnd < n_cand; cnd += kBwdThreads / 32) {
+    for (int cnd = warp; cnd < n_cand; cnd += Cfg::kThreads / 32) {
       const int q0 = (first + cnd) * 64;
       bool any = false, all = true;
       for (int rr = lane; rr < 64; rr += 32) {
@@ -306,7 +313,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
   };
 
   if (!bail && n_tiles > 0) {
-    if (warp == 4) {
+    if (warp == Cfg::kProducerWarp) {
       // ------------------------------------------------------------------ TMA producer
       bool ok = true;
       for (int j = 0; ok && j < n_tiles; ++j) {
@@ -333,7 +340,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         }
         __syncwarp();
       }
-    } else if (warp == 5) {
+    } else if (warp == Cfg::kMmaWarp) {
       // ------------------------------------------------------------------ MMA issuer
       constexpr uint32_t idesc_s = make_idesc_f16(FP16, 128, 64, false, false);
       constexpr uint32_t idesc_acc = make_idesc_f16(FP16, 128, D, false, true);
@@ -384,7 +391,9 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         if (j + 1 < n_tiles) ok = issue_s(j + 1);
         if (!ok) break;
         const int st = j % Cfg::kStages;
-        if (!warp_wait(bar_p_full, j & 1, abort_flag, prm.status)) break;
+        const int g = j % Cfg::kWGs;                  // the warpgroup that produced P / dS of this tile
+        if (!warp_wait(bar_p_full + 8 * g, (j / Cfg::kWGs) & 1, abort_flag, prm.status)) break;
+        const uint32_t pg = (uint32_t)(g * 2 * Cfg::kPBytes) >> 4;
         tc_fence_after();
         const uint32_t y0 = dym_lo + ((st * 2 * Cfg::kYBytes) >> 4);
         const uint32_t y1 = y0 + (Cfg::kYBytes >> 4);
@@ -394,28 +403,31 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             if (j == 0 && kk == 0)
-              umma_ss<false>(tmem + Cfg::kColAcc0, dds_lo + ((kk * 32) >> 4), dp_hi, y0 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
+              umma_ss<false>(tmem + Cfg::kColAcc0, dds_lo + pg + ((kk * 32) >> 4), dp_hi, y0 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
             else
-              umma_ss<true>(tmem + Cfg::kColAcc0, dds_lo + ((kk * 32) >> 4), dp_hi, y0 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
+              umma_ss<true>(tmem + Cfg::kColAcc0, dds_lo + pg + ((kk * 32) >> 4), dp_hi, y0 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
           }
           if constexpr (kDKV) {
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
               if (j == 0 && kk == 0)
-                umma_ss<false>(tmem + Cfg::kColAcc1, dp_lo + ((kk * 32) >> 4), dp_hi, y1 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
+                umma_ss<false>(tmem + Cfg::kColAcc1, dp_lo + pg + ((kk * 32) >> 4), dp_hi, y1 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
               else
-                umma_ss<true>(tmem + Cfg::kColAcc1, dp_lo + ((kk * 32) >> 4), dp_hi, y1 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
+                umma_ss<true>(tmem + Cfg::kColAcc1, dp_lo + pg + ((kk * 32) >> 4), dp_hi, y1 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
             }
           }
-          umma_commit(bar_acc_done);
+          umma_commit(bar_acc_done + 8 * g);
           umma_commit(bar_y_empty + 8 * st);
         }
         __syncwarp();
       }
     } else {
       // ------------------------------------------------------------------ softmax warps
-      const int row = tid;                            // TMEM lane, row of the stationary tile
-      const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+      const int wg = tid >> 7;                        // softmax warpgroup: takes tiles wg, wg + kWGs, ...
+      const int row = tid & 127;                      // TMEM lane, row of the stationary tile
+      const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      const uint32_t sPg = sP + wg * 2 * Cfg::kPBytes, sDSg = sDS + wg * 2 * Cfg::kPBytes;
+      const uint32_t bar_meta_g = bar_meta + 16 * wg;
       const float c = prm.scale_log2;
       const float scale = prm.sm_scale;
       const uint8_t* docs_b = nullptr;
@@ -452,7 +464,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
       int pf_lo = 0;
       long long pf_doc = 0;
       auto meta_fetch = [&](int jj) {
-        const int i = (s_tiles[jj] >> 1) * 64 + tid;
+        const int i = (s_tiles[jj] >> 1) * 64 + row;
         pf_l = 0.f, pf_dl = 0.f, pf_lo = 0, pf_doc = 0;
         if (i < prm.N) {
           pf_l = prm.lse[(size_t)bh * prm.N + i];
@@ -462,33 +474,35 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         }
       };
       auto meta_publish = [&](int jj) {
-        const int i = (s_tiles[jj] >> 1) * 64 + tid;
-        BwdMeta* mw = &s_meta[jj & 1];
+        const int i = (s_tiles[jj] >> 1) * 64 + row;
+        const int par = (jj / Cfg::kWGs) & 1;         // this warpgroup's tiles alternate buffers
+        BwdMeta* mw = &s_meta[2 * wg + par];
         int kmin = 0, kmax = -1;
         if (i < prm.N) row_interval(prm.mask, i, pf_lo, stream, kmin, kmax);
-        mw->lse[tid] = -pf_l;
-        mw->delta[tid] = -pf_dl * prm.sm_scale;
-        mw->kmin[tid] = kmin;
-        mw->kmax[tid] = kmax;
-        mw->doc[tid] = pf_doc;
-        mbar_arrive(bar_meta + 8 * (jj & 1));
+        mw->lse[row] = -pf_l;
+        mw->delta[row] = -pf_dl * prm.sm_scale;
+        mw->kmin[row] = kmin;
+        mw->kmax[row] = kmax;
+        mw->doc[row] = pf_doc;
+        mbar_arrive(bar_meta_g + 8 * par);
       };
       if constexpr (kDKV) {
-        if (tid < 64) {
-          meta_fetch(0);
-          meta_publish(0);
+        if (row < 64 && wg < n_tiles) {
+          meta_fetch(wg);
+          meta_publish(wg);
         }
       }
 
-      for (int j = 0; j < n_tiles; ++j) {
+      for (int j = wg; j < n_tiles; j += Cfg::kWGs) {
+        const int jl = j / Cfg::kWGs;                 // tiles this warpgroup has done
         bool masked;
         int y_first = 0, y_stream = 0;                // kDQ: first key token and stream of the tile
         const BwdMeta* meta = &s_meta[0];
         if constexpr (kDKV) {
           const int e = s_tiles[j];
           masked = (e & 1) != 0;
-          meta = &s_meta[j & 1];
-          if (!mbar_wait(bar_meta + 8 * (j & 1), (j >> 1) & 1, abort_flag, prm.status)) {
+          meta = &s_meta[2 * wg + (jl & 1)];
+          if (!mbar_wait(bar_meta_g + 8 * (jl & 1), (jl >> 1) & 1, abort_flag, prm.status)) {
             ok = false;
             break;
           }
@@ -504,16 +518,17 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           ok = false;
           break;
         }
-        if (j > 0) {   // P / dS buffers are free once the previous accumulation is done
-          if (!mbar_wait(bar_acc_done, (j - 1) & 1, abort_flag, prm.status)) {
+        if (jl > 0) {   // this warpgroup's P / dS tiles are free once its previous accumulation is done
+          if (!mbar_wait(bar_acc_done + 8 * wg, (jl - 1) & 1, abort_flag, prm.status)) {
             ok = false;
             break;
           }
         }
         tc_fence_after();
         if constexpr (kDKV) {
-          // every thread is past tile j-1 here, so the other meta buffer may be refilled
-          if (tid < 64 && j + 1 < n_tiles) meta_fetch(j + 1);
+          // every thread of the warpgroup is past its previous tile here, so the other meta buffer
+          // may be refilled
+          if (row < 64 && j + Cfg::kWGs < n_tiles) meta_fetch(j + Cfg::kWGs);
         }
 
         // kDQ: the visible keys of this row form an interval of the tile's 64 columns
@@ -617,11 +632,11 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           for (int q4 = 0; q4 < CH / 8; ++q4) {
             const int ch = chunk * (CH / 8) + q4;
             const uint32_t off = row * 128 + ((ch ^ (row & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDS + off), "r"(pk_ds[q4 * 4]),
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDSg + off), "r"(pk_ds[q4 * 4]),
                          "r"(pk_ds[q4 * 4 + 1]), "r"(pk_ds[q4 * 4 + 2]), "r"(pk_ds[q4 * 4 + 3])
                          : "memory");
             if constexpr (kDKV) {
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off), "r"(pk_p[q4 * 4]),
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sPg + off), "r"(pk_p[q4 * 4]),
                            "r"(pk_p[q4 * 4 + 1]), "r"(pk_p[q4 * 4 + 2]), "r"(pk_p[q4 * 4 + 3])
                            : "memory");
             }
@@ -629,15 +644,18 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         }
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(bar_p_full);
+        mbar_arrive(bar_p_full + 8 * wg);
         if constexpr (kDKV) {
-          if (tid < 64 && j + 1 < n_tiles) meta_publish(j + 1);
+          if (row < 64 && j + Cfg::kWGs < n_tiles) meta_publish(j + Cfg::kWGs);
         }
       }
 
       // ---------------------------------------------------------------- epilogue
-      if (ok) ok = mbar_wait(bar_acc_done, (n_tiles - 1) & 1, abort_flag, prm.status);
-      if (ok) {
+      // the accumulations complete in order: the last one's barrier covers them all
+      if (ok && wg == 0)
+        ok = mbar_wait(bar_acc_done + 8 * ((n_tiles - 1) % Cfg::kWGs), ((n_tiles - 1) / Cfg::kWGs) & 1,
+                       abort_flag, prm.status);
+      if (ok && wg == 0) {
         tc_fence_after();
         const size_t row_off = ((size_t)bh * prm.N + (size_t)my_row) * D * 2;
 #pragma unroll
@@ -678,9 +696,9 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
   }
 
   // the stationary tiles were requested before the plan was known: never leave with them in flight
-  if (warp == 4 && lane == 0) mbar_wait(bar_x_full, 0, abort_flag, prm.status);
+  if (warp == Cfg::kProducerWarp && lane == 0) mbar_wait(bar_x_full, 0, abort_flag, prm.status);
   __syncthreads();
-  if (warp == 4) {
+  if (warp == Cfg::kProducerWarp) {
     tc_fence_after();
     tmem_dealloc<Cfg::kTmemCols>(tmem);
   }

@@ -144,7 +144,7 @@ int launch_prefill_bwd(const CUtensorMap& x0, const CUtensorMap& x1, const CUten
   if (attr_err != cudaSuccess) return (int)attr_err;
   const long long blocks = (long long)prm.n_xtiles * prm.B * prm.H;
   if (blocks <= 0 || blocks > 0x7fffffffLL) return SPSATTN_ERR_TOO_LARGE;
-  prefill_bwd_sm100_kernel<D, FP16, MODE><<<(unsigned)blocks, kBwdThreads, Cfg::kSmemBytes, st>>>(x0, x1, y0, y1, prm);
+  prefill_bwd_sm100_kernel<D, FP16, MODE><<<(unsigned)blocks, Cfg::kThreads, Cfg::kSmemBytes, st>>>(x0, x1, y0, y1, prm);
   return (int)cudaGetLastError();
 }
 
