@@ -49,9 +49,11 @@ struct BwdParams {
   int* status;
 };
 
-template <int D>
+template <int D, int MODE>
 struct BwdCfg {
-  static constexpr int kStages = 2;
+  // ring of streamed tile pairs: a third stage where shared memory allows it (dQ mode at head_dim
+  // 128, which keeps no P tiles), so that the loads run a tile ahead of the two warpgroups
+  static constexpr int kStages = (D == 128 && MODE == kBwdDQ) ? 3 : 2;
   static constexpr int kXBytes = 128 * D * 2;
   static constexpr int kXSub = 128 * 128;
   static constexpr int kYBytes = 64 * D * 2;
@@ -67,8 +69,8 @@ struct BwdCfg {
   static constexpr int kWGs = (D == 64) ? 1 : 2;
   static constexpr int kThreads = 32 * (4 * kWGs + 2);
   static constexpr int kProducerWarp = 4 * kWGs, kMmaWarp = 4 * kWGs + 1;
-  static constexpr int kOffDS = kOffP + kPBytes;               // [warpgroup][P | dS]
-  static constexpr int kOffBar = kOffP + kWGs * 2 * kPBytes;
+  static constexpr int kPRegion = (MODE == kBwdDQ) ? kPBytes : 2 * kPBytes;   // per warpgroup: dS [| P]
+  static constexpr int kOffBar = kOffP + kWGs * kPRegion;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
   // S / dP accumulators: one pair at head_dim 64 (two blocks share the SM's 512 columns), two
   // pairs at head_dim 128 (one block per SM: the next tile's products run under this tile's softmax)
@@ -132,18 +134,18 @@ struct alignas(16) BwdMeta {   // per streamed query tile in kDKV mode: one entr
 };
 
 template <int D, bool FP16, int MODE>
-__global__ void __launch_bounds__(BwdCfg<D>::kThreads, BwdCfg<D>::kBlocksPerSM)
+__global__ void __launch_bounds__(BwdCfg<D, MODE>::kThreads, BwdCfg<D, MODE>::kBlocksPerSM)
 prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__ CUtensorMap tm_x1,
                          const __grid_constant__ CUtensorMap tm_y0, const __grid_constant__ CUtensorMap tm_y1,
                          const BwdParams prm) {
-  using Cfg = BwdCfg<D>;
+  using Cfg = BwdCfg<D, MODE>;
   constexpr bool kDKV = MODE == kBwdDKV;
   extern __shared__ uint8_t smem_raw[];
   __shared__ BlockPlan s_plan;          // kDQ: the forward's key-tile plan of this query tile
   __shared__ int s_tiles[kBwdTable];    // kDQ: packed key tiles; kDKV: (query tile << 1) | masked
   __shared__ int s_ntiles;
   __shared__ int s_cand[2];             // kDKV: first candidate query tile, number of candidates
-  __shared__ BwdMeta s_meta[kDKV ? 2 * BwdCfg<D>::kWGs : 1];   // [warpgroup][tile parity]
+  __shared__ BwdMeta s_meta[kDKV ? 2 * BwdCfg<D, MODE>::kWGs : 1];   // [warpgroup][tile parity]
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
@@ -166,17 +168,17 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
   const uint32_t sX0 = smem_base + Cfg::kOffX0;
   const uint32_t sX1 = smem_base + Cfg::kOffX1;
   const uint32_t sY = smem_base + Cfg::kOffY;
-  const uint32_t sP = smem_base + Cfg::kOffP;
-  const uint32_t sDS = smem_base + Cfg::kOffDS;
+  const uint32_t sDS = smem_base + Cfg::kOffP;              // warpgroup g: + g * kPRegion
+  const uint32_t sP = sDS + Cfg::kPBytes;                   // kDKV only
   const uint32_t bar0 = smem_base + Cfg::kOffBar;
   const uint32_t bar_x_full = bar0;
-  const uint32_t bar_y_full = bar0 + 8;      // [2]
-  const uint32_t bar_y_empty = bar0 + 24;    // [2]
-  const uint32_t bar_s_full = bar0 + 40;     // [2]
-  const uint32_t bar_s_free = bar0 + 56;     // [2]
-  const uint32_t bar_p_full = bar0 + 72;     // [warpgroup]
-  const uint32_t bar_acc_done = bar0 + 88;   // [warpgroup]
-  const uint32_t bar_meta = bar0 + 104;      // [warpgroup][2]
+  const uint32_t bar_y_full = bar0 + 8;      // [kStages <= 4]
+  const uint32_t bar_y_empty = bar0 + 40;    // [kStages <= 4]
+  const uint32_t bar_s_full = bar0 + 72;     // [2]
+  const uint32_t bar_s_free = bar0 + 88;     // [2]
+  const uint32_t bar_p_full = bar0 + 104;    // [warpgroup]
+  const uint32_t bar_acc_done = bar0 + 120;  // [warpgroup]
+  const uint32_t bar_meta = bar0 + 136;      // [warpgroup][2]
 
   const bool has_docs = prm.docs != nullptr;
   const bool general = has_docs && prm.mono != nullptr && prm.mono[b] == 0;
@@ -233,9 +235,11 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
   if (warp == Cfg::kProducerWarp) {
     if (lane == 0) {
       mbar_init(bar_x_full, 1);
-      for (int s = 0; s < 2; ++s) {
+      for (int s = 0; s < Cfg::kStages; ++s) {
         mbar_init(bar_y_full + 8 * s, 1);
         mbar_init(bar_y_empty + 8 * s, 1);
+      }
+      for (int s = 0; s < 2; ++s) {
         mbar_init(bar_meta + 8 * s, 64);
         mbar_init(bar_meta + 16 + 8 * s, 64);
         mbar_init(bar_p_full + 8 * s, 128);
@@ -393,7 +397,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         const int st = j % Cfg::kStages;
         const int g = j % Cfg::kWGs;                  // the warpgroup that produced P / dS of this tile
         if (!warp_wait(bar_p_full + 8 * g, (j / Cfg::kWGs) & 1, abort_flag, prm.status)) break;
-        const uint32_t pg = (uint32_t)(g * 2 * Cfg::kPBytes) >> 4;
+        const uint32_t pg = (uint32_t)(g * Cfg::kPRegion) >> 4;
         tc_fence_after();
         const uint32_t y0 = dym_lo + ((st * 2 * Cfg::kYBytes) >> 4);
         const uint32_t y1 = y0 + (Cfg::kYBytes >> 4);
@@ -426,7 +430,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
       const int wg = tid >> 7;                        // softmax warpgroup: takes tiles wg, wg + kWGs, ...
       const int row = tid & 127;                      // TMEM lane, row of the stationary tile
       const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-      const uint32_t sPg = sP + wg * 2 * Cfg::kPBytes, sDSg = sDS + wg * 2 * Cfg::kPBytes;
+      const uint32_t sPg = sP + wg * Cfg::kPRegion, sDSg = sDS + wg * Cfg::kPRegion;
       const uint32_t bar_meta_g = bar_meta + 16 * wg;
       const float c = prm.scale_log2;
       const float scale = prm.sm_scale;

@@ -134,7 +134,7 @@ int launch_prefill_sm100(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
 template <int D, bool FP16, int MODE>
 int launch_prefill_bwd(const CUtensorMap& x0, const CUtensorMap& x1, const CUtensorMap& y0,
                        const CUtensorMap& y1, const BwdParams& prm, cudaStream_t st) {
-  using Cfg = BwdCfg<D>;
+  using Cfg = BwdCfg<D, MODE>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
