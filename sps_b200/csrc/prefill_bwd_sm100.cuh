@@ -53,7 +53,7 @@ template <int D, int MODE>
 struct BwdCfg {
   // ring of streamed tile pairs: a third stage where shared memory allows it (dQ mode at head_dim
   // 128, which keeps no P tiles), so that the loads run a tile ahead of the two warpgroups
-  static constexpr int kStages = (D == 128 && MODE == kBwdDQ) ? 3 : 2;
+  static constexpr int kStages = (D == 128) ? (MODE == kBwdDQ ? 3 : 4) : 2;
   static constexpr int kXBytes = 128 * D * 2;
   static constexpr int kXSub = 128 * 128;
   static constexpr int kYBytes = 64 * D * 2;
@@ -69,7 +69,13 @@ struct BwdCfg {
   static constexpr int kWGs = (D == 64) ? 1 : 2;
   static constexpr int kThreads = 32 * (4 * kWGs + 2);
   static constexpr int kProducerWarp = 4 * kWGs, kMmaWarp = 4 * kWGs + 1;
-  static constexpr int kPRegion = (MODE == kBwdDQ) ? kPBytes : 2 * kPBytes;   // per warpgroup: dS [| P]
+  // dK/dV mode at head_dim 128: P^T and dS^T never touch shared memory.  The softmax thread of a
+  // key row writes them (packed 16-bit pairs) over the S^T / dP^T columns it has just read, and the
+  // accumulating MMAs take them from tensor memory as their A operand; the 64 KB this frees hold
+  // two more ring stages.  It needs the two S / dP pairs: the next product into the same pair is
+  // issued after this tile's accumulation, and the tensor pipe runs in issue order.
+  static constexpr bool kPTmem = (D == 128 && MODE == kBwdDKV);
+  static constexpr int kPRegion = kPTmem ? 0 : (MODE == kBwdDQ) ? kPBytes : 2 * kPBytes;   // per warpgroup: dS [| P]
   static constexpr int kOffBar = kOffP + kWGs * kPRegion;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
   // S / dP accumulators: one pair at head_dim 64 (two blocks share the SM's 512 columns), two
@@ -404,6 +410,18 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         if (elect_one()) {
           // dS (and P): K-major A, 16 of the 64 streamed rows = 32 bytes per step; Y: MN-major B,
           // 16 rows = 2048 bytes per step
+          if constexpr (Cfg::kPTmem) {
+            // A from tensor memory: 16 contraction elements = 8 columns per step
+            const uint32_t ta = tmem + g * Cfg::kSBufCols;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_ts(tmem + Cfg::kColAcc0, ta + Cfg::kColDP + 8 * kk, y0 + ((kk * 2048) >> 4), dym_hi, idesc_acc,
+                      !(j == 0 && kk == 0));
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_ts(tmem + Cfg::kColAcc1, ta + Cfg::kColS + 8 * kk, y1 + ((kk * 2048) >> 4), dym_hi, idesc_acc,
+                      !(j == 0 && kk == 0));
+          } else {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             if (j == 0 && kk == 0)
@@ -419,6 +437,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
               else
                 umma_ss<true>(tmem + Cfg::kColAcc1, dp_lo + pg + ((kk * 32) >> 4), dp_hi, y1 + ((kk * 2048) >> 4), dym_hi, idesc_acc);
             }
+          }
           }
           umma_commit(bar_acc_done + 8 * g);
           umma_commit(bar_y_empty + 8 * st);
@@ -630,10 +649,16 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
             pk_p[e / 2] = pack2<FP16>(p.x, p.y);
             pk_ds[e / 2] = pack2<FP16>(ds.x, ds.y);
           }
+          if constexpr (Cfg::kPTmem) {
+            // over the columns of S^T / dP^T this warp has already read: chunk c (16 columns of
+            // each) leaves 8 packed columns of P^T at S^T + 8c and of dS^T at dP^T + 8c
+            tmem_st8(ts + Cfg::kColS + chunk * (CH / 2), pk_p);
+            tmem_st8(ts + Cfg::kColDP + chunk * (CH / 2), pk_ds);
+          }
           // K-major 128B-swizzled [128 x 64] tiles: 16-byte chunk ch of row r sits at
           // r * 128 + ((ch ^ (r & 7)) << 4)
 #pragma unroll
-          for (int q4 = 0; q4 < CH / 8; ++q4) {
+          for (int q4 = 0; q4 < (Cfg::kPTmem ? 0 : CH / 8); ++q4) {
             const int ch = chunk * (CH / 8) + q4;
             const uint32_t off = row * 128 + ((ch ^ (row & 7)) << 4);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDSg + off), "r"(pk_ds[q4 * 4]),
@@ -646,7 +671,8 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
             }
           }
         }
-        fence_proxy_async_smem();
+        if constexpr (Cfg::kPTmem) tmem_wait_st();
+        else fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(bar_p_full + 8 * wg);
         if constexpr (kDKV) {
