@@ -51,9 +51,9 @@ struct BwdParams {
 
 template <int D, int MODE>
 struct BwdCfg {
-  // ring of streamed tile pairs: a third stage where shared memory allows it (dQ mode at head_dim
-  // 128, which keeps no P tiles), so that the loads run a tile ahead of the two warpgroups
-  static constexpr int kStages = (D == 128) ? (MODE == kBwdDQ ? 3 : 4) : 2;
+  // ring of streamed tile pairs: four stages at head_dim 128 (P / dS live in tensor memory there,
+  // see kPTmem), so that the loads run ahead of the two warpgroups
+  static constexpr int kStages = (D == 128) ? 4 : 2;
   static constexpr int kXBytes = 128 * D * 2;
   static constexpr int kXSub = 128 * 128;
   static constexpr int kYBytes = 64 * D * 2;
@@ -69,12 +69,11 @@ struct BwdCfg {
   static constexpr int kWGs = (D == 64) ? 1 : 2;
   static constexpr int kThreads = 32 * (4 * kWGs + 2);
   static constexpr int kProducerWarp = 4 * kWGs, kMmaWarp = 4 * kWGs + 1;
-  // dK/dV mode at head_dim 128: P^T and dS^T never touch shared memory.  The softmax thread of a
-  // key row writes them (packed 16-bit pairs) over the S^T / dP^T columns it has just read, and the
+  // head_dim 128: P and dS never touch shared memory.  The softmax thread of a row writes them (packed 16-bit pairs) over the S^T / dP^T columns it has just read, and the
   // accumulating MMAs take them from tensor memory as their A operand; the 64 KB this frees hold
   // two more ring stages.  It needs the two S / dP pairs: the next product into the same pair is
   // issued after this tile's accumulation, and the tensor pipe runs in issue order.
-  static constexpr bool kPTmem = (D == 128 && MODE == kBwdDKV);
+  static constexpr bool kPTmem = (D == 128);
   static constexpr int kPRegion = kPTmem ? 0 : (MODE == kBwdDQ) ? kPBytes : 2 * kPBytes;   // per warpgroup: dS [| P]
   static constexpr int kOffBar = kOffP + kWGs * kPRegion;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
@@ -417,10 +416,12 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
             for (int kk = 0; kk < 4; ++kk)
               umma_ts(tmem + Cfg::kColAcc0, ta + Cfg::kColDP + 8 * kk, y0 + ((kk * 2048) >> 4), dym_hi, idesc_acc,
                       !(j == 0 && kk == 0));
+            if constexpr (kDKV) {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              umma_ts(tmem + Cfg::kColAcc1, ta + Cfg::kColS + 8 * kk, y1 + ((kk * 2048) >> 4), dym_hi, idesc_acc,
-                      !(j == 0 && kk == 0));
+              for (int kk = 0; kk < 4; ++kk)
+                umma_ts(tmem + Cfg::kColAcc1, ta + Cfg::kColS + 8 * kk, y1 + ((kk * 2048) >> 4), dym_hi, idesc_acc,
+                        !(j == 0 && kk == 0));
+            }
           } else {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
@@ -650,10 +651,13 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
             pk_ds[e / 2] = pack2<FP16>(ds.x, ds.y);
           }
           if constexpr (Cfg::kPTmem) {
-            // over the columns of S^T / dP^T this warp has already read: chunk c (16 columns of
-            // each) leaves 8 packed columns of P^T at S^T + 8c and of dS^T at dP^T + 8c
-            tmem_st8(ts + Cfg::kColS + chunk * (CH / 2), pk_p);
-            tmem_st8(ts + Cfg::kColDP + chunk * (CH / 2), pk_ds);
+            // over the columns of S / dP this warp has already read: chunk c (CH columns of each)
+            // leaves CH / 2 packed columns of P at S + c * CH / 2 and of dS at dP + c * CH / 2
+#pragma unroll
+            for (int q8 = 0; q8 < CH / 16; ++q8) {
+              if constexpr (kDKV) tmem_st8(ts + Cfg::kColS + chunk * (CH / 2) + 8 * q8, pk_p + 8 * q8);
+              tmem_st8(ts + Cfg::kColDP + chunk * (CH / 2) + 8 * q8, pk_ds + 8 * q8);
+            }
           }
           // K-major 128B-swizzled [128 x 64] tiles: 16-byte chunk ch of row r sits at
           // r * 128 + ((ch ^ (r & 7)) << 4)
