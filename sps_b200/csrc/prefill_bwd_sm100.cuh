@@ -53,7 +53,7 @@ template <int D, int MODE>
 struct BwdCfg {
   // ring of streamed tile pairs: four stages at head_dim 128 (P / dS live in tensor memory there,
   // see kPTmem), so that the loads run ahead of the two warpgroups
-  static constexpr int kStages = (D == 128) ? 4 : 2;
+  static constexpr int kStages = 4;
   static constexpr int kXBytes = 128 * D * 2;
   static constexpr int kXSub = 128 * 128;
   static constexpr int kYBytes = 64 * D * 2;
@@ -73,7 +73,7 @@ struct BwdCfg {
   // accumulating MMAs take them from tensor memory as their A operand; the 64 KB this frees hold
   // two more ring stages.  It needs the two S / dP pairs: the next product into the same pair is
   // issued after this tile's accumulation, and the tensor pipe runs in issue order.
-  static constexpr bool kPTmem = (D == 128);
+  static constexpr bool kPTmem = true;
   static constexpr int kPRegion = kPTmem ? 0 : (MODE == kBwdDQ) ? kPBytes : 2 * kPBytes;   // per warpgroup: dS [| P]
   static constexpr int kOffBar = kOffP + kWGs * kPRegion;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
@@ -397,7 +397,10 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
       bool ok = warp_wait(bar_x_full, 0, abort_flag, prm.status);
       if (ok) ok = issue_s(0);
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) ok = issue_s(j + 1);
+        // with P / dS laid over a single S / dP pair the next products may only be issued after this
+        // tile's accumulation (the tensor pipe runs in issue order)
+        constexpr bool kAhead = !(Cfg::kPTmem && Cfg::kSBufs == 1);
+        if (kAhead && j + 1 < n_tiles) ok = issue_s(j + 1);
         if (!ok) break;
         const int st = j % Cfg::kStages;
         const int g = j % Cfg::kWGs;                  // the warpgroup that produced P / dS of this tile
@@ -444,6 +447,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           umma_commit(bar_y_empty + 8 * st);
         }
         __syncwarp();
+        if (!kAhead && j + 1 < n_tiles) ok = issue_s(j + 1);
       }
     } else {
       // ------------------------------------------------------------------ softmax warps
