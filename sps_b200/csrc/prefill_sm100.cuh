@@ -78,6 +78,13 @@ struct PrefillCfg {
   static constexpr int kOffBar = kOffP + kPBytes;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;      // barriers + alignment slack
   static constexpr int kBlocksPerSM = (D == 64) ? 3 : 2;
+  // head_dim 128 (two S accumulators): P never touches shared memory.  The softmax thread writes
+  // it, as packed 16-bit pairs, over the S columns it has just read, and the P V product takes it
+  // from tensor memory as its A operand, which also halves what that product reads from shared
+  // memory.  The next Q K^T into the same accumulator is issued after this tile's P V, and the
+  // tensor pipe runs in issue order.  (With the single accumulator of head_dim 64 the next Q K^T
+  // would have to wait for P V; measured slower there.)
+  static constexpr bool kPTmem = (D == 128);
 };
 
 struct TileInfo {
@@ -343,14 +350,22 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           const uint32_t od = tmem + Cfg::kColO;
           if (elect_one()) {
             // P: K-major, one 64-key sub-tile; V: MN-major, 16 key rows = 2048 bytes per step
-            if (j > 0) {
-              umma_ss<true>(od, dp_lo, dp_hi, vb0, dv_hi, idesc_pv);
-            } else {
-              umma_ss<false>(od, dp_lo, dp_hi, vb0, dv_hi, idesc_pv);
-            }
+            if constexpr (Cfg::kPTmem) {
+              // A from tensor memory: 16 keys = 8 packed columns per step
+              const uint32_t pa = tmem + (j % Cfg::kSBufs) * kTileN;
 #pragma unroll
-            for (int kk = 1; kk < kTileN / 16; ++kk)
-              umma_ss<true>(od, dp_lo + ((kk * 32) >> 4), dp_hi, vb0 + ((kk * 2048) >> 4), dv_hi, idesc_pv);
+              for (int kk = 0; kk < kTileN / 16; ++kk)
+                umma_ts(od, pa + 8 * kk, vb0 + ((kk * 2048) >> 4), dv_hi, idesc_pv, j > 0 || kk > 0);
+            } else {
+              if (j > 0) {
+                umma_ss<true>(od, dp_lo, dp_hi, vb0, dv_hi, idesc_pv);
+              } else {
+                umma_ss<false>(od, dp_lo, dp_hi, vb0, dv_hi, idesc_pv);
+              }
+#pragma unroll
+              for (int kk = 1; kk < kTileN / 16; ++kk)
+                umma_ss<true>(od, dp_lo + ((kk * 32) >> 4), dp_hi, vb0 + ((kk * 2048) >> 4), dv_hi, idesc_pv);
+            }
             umma_commit(bar_pv_done);
             umma_commit(bar_v_empty + 8 * st);
           }
@@ -495,7 +510,10 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         l_run += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         if (tid == 0) SPS_TRACE(j, 4);
 
-        if (j > 0) {  // P buffer free and O stable once the previous P V product is done
+        // the shared-memory P tile is free, and O may be rescaled, once the previous P V product is
+        // done; P in tensor memory needs no wait (the S this thread read was written after the
+        // last product that read these columns, in issue order)
+        if (j > 0 && (!Cfg::kPTmem || rescale)) {
           if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag, prm.status)) {
             ok = false;
             break;
@@ -503,10 +521,15 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           tc_fence_after();
         }
         if (tid == 0) SPS_TRACE(j, 5);
+        if constexpr (Cfg::kPTmem) {
+#pragma unroll
+          for (int q8 = 0; q8 < kTileN / 16; ++q8)
+            tmem_st8(tmem + lane_addr + sb * kTileN + 8 * q8, pk + 8 * q8);
+        }
         // P -> shared memory, K-major 128B-swizzled: 16-byte chunk ch of row r sits at
         // r * 128 + ((ch ^ (r & 7)) << 4) of the [128 x 64] tile
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        for (int ch = 0; ch < (Cfg::kPTmem ? 0 : 8); ++ch) {
           const uint32_t addr = sP + row * 128 + ((ch ^ (row & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[ch * 4]),
                        "r"(pk[ch * 4 + 1]), "r"(pk[ch * 4 + 2]), "r"(pk[ch * 4 + 3])
@@ -526,7 +549,8 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           tmem_wait_st();
         }
         if (tid == 0) SPS_TRACE(j, 7);
-        fence_proxy_async_smem();
+        if constexpr (Cfg::kPTmem) tmem_wait_st();
+        else fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(bar_p_full);
         if (tid == 0) SPS_TRACE(j, 8);
