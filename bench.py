@@ -281,10 +281,11 @@ def run_ours(args):
         b_flops = 2.5 * wl.flops
         tb = b_flops / (b_launch * 1e-3) / 1e12
         result["prefill_backward"] = {
-            "workload": f"{PREFILL}: dQ, dK, dV of the same batch from dO (delta pre-pass + dK/dV kernel + "
+            "workload": f"{PREFILL}: dQ, dK, dV of the same batch from dO (pre-passes + dK/dV kernel + "
                         "dQ kernel per step), per GPU",
             "useful_gflop_per_step_per_gpu": b_flops / 1e9, "ms_per_step": b_region / kb,
-            "useful_tflops": world * b_flops * kb / (b_region * 1e-3) / 1e12, "gpu_launches": 4 * kb,
+            "useful_tflops": world * b_flops * kb / (b_region * 1e-3) / 1e12,
+            "gpu_launches": 5 * kb,      # document pre-pass, run ends, delta, dK/dV, dQ
             "roofline": {"bound": "tensor", "achieved": tb, "peak": peak, "unit": "TFLOP/s", "frac": tb / peak,
                          "traffic": None, "peak_source": f"{peak_kind} bf16 burst", "launch_ms": b_launch,
                          "note": "useful FLOPs = 2.5 x forward; the two kernels recompute S and dP, so they "

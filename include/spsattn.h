@@ -119,7 +119,7 @@ int spsattn_prefill_fwd_strided(const void* q, const void* k, const void* v, voi
  * probabilities recomputed from `lse` as written by the forward call on the same q, k, v, mask and
  * sm_scale (the reference's backward, triton_sps_flash_attention.py:623-720, does the same with
  * its M tensor).  All tensors dense [B, H, N, D] of `dtype`; `o` is the forward output; lse is
- * [B, H, N] fp32.  Three launches: delta = rowsum(d_o * o), then dk / dv (one block per 128-token
+ * [B, H, N] fp32.  Launches (after the document pre-passes, if ids are given): delta = rowsum(d_o * o), then dk / dv (one block per 128-token
  * key tile of each parity stream, visiting only the query tiles that can see it), then dq (one
  * block per 128-row query tile, visiting the key tiles the forward visits).  D in {64, 128};
  * N <= 65536.  workspace: spsattn_prefill_bwd_workspace_bytes(B, H, N, D) bytes, 256-byte aligned. */

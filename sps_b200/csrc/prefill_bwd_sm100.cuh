@@ -16,6 +16,10 @@
 //   P  = exp2(S * scale*log2e - lse),  dS = P * (dP - delta) * scale     softmax warps, registers
 //   acc0 += dS Y0  (dQ += dS K,  or dK += dS^T Q)         tcgen05.mma 128xDx64, Y as MN-major B
 //   acc1 += P  Y1  (kDKV only: dV += P^T dO)
+// P and dS are written back to tensor memory (packed 16-bit pairs over the S / dP columns already
+// read) and enter the accumulating MMAs as their A operand from there; shared memory only holds
+// the operand tiles delivered by TMA.  Head_dim 64: four softmax warps, two blocks per SM; head_dim
+// 128: two softmax warpgroups taking alternate tiles, one block per SM with all 512 columns.
 // The visibility rule is the forward's: every mask bit comes from row_interval().
 #pragma once
 
