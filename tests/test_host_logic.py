@@ -53,11 +53,25 @@ def test_argument_errors_are_reported_before_any_launch():
     assert lib.spsattn_decode_fwd(fake, 2, fake, None, 0, None, 0, 1, 1, 64, 0, 0.125, None, 0, None, None) == -4
     assert lib.spsattn_kv_update(*([None] * 12), 1, 1, 64, 0, 4, 0, 2, None) == -1
     assert "unknown" not in err(-7)
+    # the backward entry point: q, k, v, o, d_o, lse, dq, dk, dv, then the forward's arguments
+    bargs = lambda **kw: [fake] * 9 + [None, 0, 0, 0, 1, 1, kw.get("N", 8), kw.get("D", 64), kw.get("dtype", 0),
+                                        kw.get("scale", 0.125), kw.get("parity", 0), 1, _lib.NO_WINDOW, 0,
+                                        kw.get("ws", None), kw.get("ws_bytes", 0), None, None]
+    assert lib.spsattn_prefill_bwd(*([None] * 9 + bargs()[9:])) == -1
+    assert lib.spsattn_prefill_bwd(*bargs(D=32)) == -2          # backward kernels: head_dim 64 and 128
+    assert lib.spsattn_prefill_bwd(*bargs(N=7)) == -5
+    assert lib.spsattn_prefill_bwd(*bargs(N=2 * 65536)) == -7
+    assert lib.spsattn_prefill_bwd(*bargs(scale=-1.0)) == -1
+    assert lib.spsattn_prefill_bwd(*bargs()) == -4               # workspace missing
+    assert lib.spsattn_prefill_bwd(*bargs(ws=fake, ws_bytes=16)) == -4
 
 
 def test_workspace_sizes():
     lib = _lib.load()
     assert lib.spsattn_prefill_workspace_bytes(8, 12, 8192, 64) >= 8 * 8192 * 4 + 8 * 4
+    # backward: the forward's pre-pass arrays + delta [B, H, N] fp32 + run ends [B, N] int32
+    assert (lib.spsattn_prefill_bwd_workspace_bytes(8, 12, 8192, 64)
+            >= lib.spsattn_prefill_workspace_bytes(8, 12, 8192, 64) + 8 * 12 * 8192 * 4 + 8 * 8192 * 4)
     seg = (_lib.Segment * 2)()
     seg[0].max_rows, seg[1].max_rows = 64, 4096
     need = lib.spsattn_decode_workspace_bytes(128, 16, 64, 2, seg, 2)
