@@ -39,6 +39,9 @@ GENERATION = "cfg3_xl_generation"
 # processed (traffic is proportional to batch rows / sequences)
 PREFILL_DRAM_BYTES_PER_LAUNCH = 2 * (151.4e6 + 33.3e6)
 DECODE_DRAM_BYTES_PER_LAUNCH = 4 * (332.2e6 + 4.9e6)
+# dK/dV kernel + dQ kernel of one backward call: ncu dram bytes of a 4-row call x2
+# (profiles/prefill_bwd_sm100_d64_cfg1_half_batch.md)
+BACKWARD_DRAM_BYTES_PER_CALL = 2 * (204.8e6 + 76.8e6 + 204.7e6 + 36.4e6)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -287,7 +290,10 @@ def run_ours(args):
             "useful_tflops": world * b_flops * kb / (b_region * 1e-3) / 1e12,
             "gpu_launches": 5 * kb,      # document pre-pass, run ends, delta, dK/dV, dQ
             "roofline": {"bound": "tensor", "achieved": tb, "peak": peak, "unit": "TFLOP/s", "frac": tb / peak,
-                         "traffic": None, "peak_source": f"{peak_kind} bf16 burst", "launch_ms": b_launch,
+                         "traffic": BACKWARD_DRAM_BYTES_PER_CALL,
+                         "traffic_source": "ncu dram__bytes_read+write of the two kernels of a 4-row call x2 "
+                                           "(profiles/prefill_bwd_sm100_d64_cfg1_half_batch.md)",
+                         "peak_source": f"{peak_kind} bf16 burst", "launch_ms": b_launch,
                          "note": "useful FLOPs = 2.5 x forward; the two kernels recompute S and dP, so they "
                                  "execute 3.5 x forward"},
         }

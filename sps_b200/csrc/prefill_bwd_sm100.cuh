@@ -290,21 +290,34 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
     for (int j = tid; j < min(s_plan.n_tiles, kBwdTable); j += Cfg::kThreads)
       s_tiles[j] = pack_tile(tile_info(s_plan, j));
   } else {
-    // per candidate query tile: does any row see any key of this tile, do all rows see all keys
+    // Per candidate query tile, one thread each: can a row see a key of this tile, do all rows see
+    // all keys.  Within a tile the visible interval [kmin, kmax] of a row moves up monotonically
+    // with the row (causal bound, window bound and run start all do), so the first and the last
+    // row decide: the tile is interior iff the last row's kmin and the first row's kmax cover the
+    // key tile, and it may be skipped if the last row's kmax or the first row's kmin misses it
+    // (a superset of the truly visible tiles: a tile kept in vain is fully masked and adds zeros).
+    // Streams only one row parity can see are never interior.
     const int first = s_cand[0], n_cand = s_cand[1];
-    for (int cnd = warp; cnd < n_cand; cnd += Cfg::kThreads / 32) {
+    int only;
+    const bool filt = stream_row_filter(prm.mask, stream, only);
+    for (int cnd = tid; cnd < n_cand; cnd += Cfg::kThreads) {
       const int q0 = (first + cnd) * 64;
-      bool any = false, all = true;
-      for (int rr = lane; rr < 64; rr += 32) {
-        const int i = q0 + rr;
-        int kmin = 0, kmax = -1;
-        if (i < prm.N) row_interval(prm.mask, i, lo_b != nullptr ? lo_b[i] : 0, stream, kmin, kmax);
-        any |= max(kmin, x0) <= min(kmax, x0 + 127);
-        all &= kmin <= x0 && kmax >= x0 + 127;
+      int ra = q0, rb = min(q0 + 63, prm.N - 1);
+      const bool partial = q0 + 63 > prm.N - 1;
+      if (filt) {
+        if ((ra & 1) != only) ++ra;
+        if ((rb & 1) != only) --rb;
       }
-      any = __any_sync(0xffffffffu, any);
-      all = __all_sync(0xffffffffu, all);
-      if (lane == 0) s_tiles[cnd] = any ? (((first + cnd) << 1) | ((all && !general) ? 0 : 1)) : -1;
+      int e = -1;
+      if (ra <= rb) {
+        int kmin_a, kmax_a, kmin_b, kmax_b;
+        row_interval(prm.mask, ra, lo_b != nullptr ? lo_b[ra] : 0, stream, kmin_a, kmax_a);
+        row_interval(prm.mask, rb, lo_b != nullptr ? lo_b[rb] : 0, stream, kmin_b, kmax_b);
+        const bool any = kmax_b >= x0 && kmin_a <= x0 + 127;
+        const bool all = !filt && !partial && !general && kmin_b <= x0 && kmax_a >= x0 + 127;
+        if (any) e = ((first + cnd) << 1) | (all ? 0 : 1);
+      }
+      s_tiles[cnd] = e;
     }
     __syncthreads();
     if (tid == 0) {
