@@ -133,6 +133,7 @@ class _PrefillAttention(torch.autograd.Function):
         return o
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, d_o):
         q, k, v, o, lse = ctx.saved_tensors
         sm_scale, parity, tw, pw, flags = ctx.args

@@ -14,7 +14,7 @@ import torch
 from torch import Tensor
 
 from . import _lib
-from .attention import _dtype_code, _status
+from .attention import _dtype_code, _forward_only, _status
 
 
 @dataclass
@@ -99,6 +99,8 @@ def decode_attention(
     lib = _lib.load()
     if not q.is_cuda:
         raise RuntimeError("CUDA tensors are required for segmented decode attention")
+    # decode is the generation path: no backward kernels behind it
+    _forward_only(q, *[t for seg in segments for t in (seg.k, seg.v)], *[t for e in extras for t in e[:2]])
     S, nq, H, D = q.shape
     q = q.contiguous()
     dt = _dtype_code(q)

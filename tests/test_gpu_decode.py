@@ -209,6 +209,10 @@ def test_decode_argument_errors():
         sps_b200.segmented_q2_attention(q.cpu(), [sps_b200.KVSegment(k, k, ln)], **kw)
     with pytest.raises(RuntimeError):
         sps_b200.segmented_q2_attention(q, [sps_b200.KVSegment(k, k, ln.cpu())], **kw)
+    with pytest.raises(RuntimeError, match="forward only"):          # no backward behind decode
+        sps_b200.segmented_q2_attention(q.clone().requires_grad_(True), [sps_b200.KVSegment(k, k, ln)], **kw)
+    with torch.no_grad():
+        sps_b200.segmented_q2_attention(q.clone().requires_grad_(True), [sps_b200.KVSegment(k, k, ln)], **kw)
 
 
 @pytest.mark.parametrize("tag", ["ds", "sps"])
