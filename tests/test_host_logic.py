@@ -201,3 +201,80 @@ def test_generator_refuses_to_work_without_cuda_extension_inputs():
     with _pytest.raises(ValueError):
         _validate_left_padded(torch.tensor([[62, 62]]), 62, "prompts")
     assert SPSDims(32, 64, 2, 2, 128, 256).head_dim == 64
+
+
+def _row_interval(n, ks, parity, w, pw, flags, i, lo_i, p):
+    """row_interval() of sps_b200/csrc/mask.cuh restated (same arithmetic as _host_intervals)."""
+    if i >= n:
+        return 0, -1
+    if ks == 1:
+        return lo_i, i
+    kmax, kmin, ti = (i - p) >> 1, (lo_i - p + 1) >> 1, i >> 1
+    if p == parity:
+        if pw is not None:
+            if pw >= 0:
+                kmin = max(kmin, ti - pw)
+            elif (i & 1) == p:
+                kmin = kmax = ti
+            else:
+                kmin, kmax = 0, -1
+    else:
+        kmin = max(kmin, ti - w)
+        if (flags & 1) and (i & 1) == parity:
+            kmin, kmax = 0, -1
+    return kmin, kmax
+
+
+def test_backward_tile_classification_from_first_and_last_row():
+    """The dK/dV kernel decides from the first and last row of a 64-row query tile whether the
+    tile sees a 128-token key tile at all and whether it sees all of it
+    (sps_b200/csrc/prefill_bwd_sm100.cuh).  Against the dense mask: every needed tile is kept,
+    none is kept in vain, and a tile called interior is fully visible."""
+    rng = np.random.default_rng(0)
+    kept = needed = 0
+    for _ in range(120):
+        parity = int(rng.choice([0, 1, -1]))
+        ks = 1 if parity < 0 else 2
+        n = int(rng.integers(1, 400)) * ks
+        w = min(int(rng.choice([0, 1, 3, 17, 64, 200, n])), n)
+        pw = None if parity < 0 or rng.random() < 0.5 else int(rng.choice([-1, 0, 2, 40]))
+        flags = int(rng.random() < 0.3) if parity >= 0 else 0
+        t = n // ks
+        docs = None
+        if rng.random() < 0.7:
+            ids, d, mean = [], 0, int(rng.choice([3, 20, 150]))
+            while len(ids) < t:
+                ids += [d] * int(rng.geometric(1.0 / mean))
+                d += 1
+            docs = np.repeat(np.array(ids[:t]), ks)
+        vis = orc.visible_mask(n, persistent_parity=parity, temporary_window=w, persistent_window=pw,
+                               docs_row=docs, mask_flags=flags)
+        lo = np.zeros(n, dtype=np.int64) if docs is None else orc.run_starts(docs)
+        for stream in range(ks):
+            filt, only = False, -1                       # stream_row_filter() of mask.cuh
+            if ks == 2 and stream == parity and pw is not None and pw < 0:
+                filt, only = True, stream
+            elif ks == 2 and stream != parity and (flags & 1):
+                filt, only = True, 1 - parity
+            for x0 in range(0, t, 128):
+                keys = [ks * kt + stream for kt in range(x0, min(x0 + 128, t))]
+                for q0 in range(0, n, 64):
+                    rows = list(range(q0, min(q0 + 64, n)))
+                    sub = vis[np.ix_(rows, keys)]
+                    t_any = bool(sub.any())
+                    t_all = bool(sub.all()) and len(rows) == 64 and len(keys) == 128
+                    ra, rb = q0, min(q0 + 63, n - 1)
+                    if filt:
+                        ra += int((ra & 1) != only)
+                        rb -= int((rb & 1) != only)
+                    f_any = f_all = False
+                    if ra <= rb:
+                        kmin_a, kmax_a = _row_interval(n, ks, parity, w, pw, flags, ra, int(lo[ra]), stream)
+                        kmin_b, kmax_b = _row_interval(n, ks, parity, w, pw, flags, rb, int(lo[rb]), stream)
+                        f_any = kmax_b >= x0 and kmin_a <= x0 + 127
+                        f_all = (not filt) and q0 + 63 <= n - 1 and kmin_b <= x0 and kmax_a >= x0 + 127
+                    assert f_any or not t_any, (parity, n, w, pw, flags, stream, x0, q0)
+                    assert t_all or not f_all, (parity, n, w, pw, flags, stream, x0, q0)
+                    kept += f_any
+                    needed += t_any
+    assert kept == needed and needed > 500
