@@ -134,6 +134,21 @@ int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void*
                         void* workspace, size_t workspace_bytes,
                         int* device_status, void* stream);
 
+/* The same on operands that are not dense blocks (the token-major views the reference's modules
+ * pass, src/modeling/models/sps/core.py:45-55, and the gradients autograd hands back for them):
+ * `strides` holds eight (batch, head, row) triples in elements, in the order q, k, v, o, d_o, dq,
+ * dk, dv; rows are D contiguous elements, every stride a multiple of 8 and >= D.  The reference's
+ * backward copies all of them first (triton_sps_flash_attention.py:629-633). */
+int spsattn_prefill_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                const float* lse, void* dq, void* dk, void* dv, const int64_t* strides,
+                                const void* doc_ids, int doc_is_i64, int64_t doc_stride_b,
+                                int64_t doc_stride_t,
+                                int B, int H, int N, int D, int dtype, float sm_scale,
+                                int persistent_parity, int temporary_window, int persistent_window,
+                                int mask_flags,
+                                void* workspace, size_t workspace_bytes,
+                                int* device_status, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Decode: nq (1 or 2) queries per (sequence, head) over up to 3 length-masked KV segments plus up
  * to 2 single-token "current" K/V entries; fp32 output [S, nq, H, D].

@@ -25,7 +25,7 @@ EXPORTS = (
     "spsattn_kv_update", "spsattn_fill_decode_caches", "spsattn_rope_cast", "spsattn_debug_visibility",
     "spsattn_decode_step_workspace_bytes", "spsattn_decode_step", "spsattn_qkv_rope_cast",
     "spsattn_add_rmsnorm", "spsattn_swiglu", "spsattn_debug_decode_path",
-    "spsattn_prefill_bwd_workspace_bytes", "spsattn_prefill_bwd",
+    "spsattn_prefill_bwd_workspace_bytes", "spsattn_prefill_bwd", "spsattn_prefill_bwd_strided",
 )
 
 
@@ -95,6 +95,9 @@ def load() -> C.CDLL:
     lib.spsattn_prefill_bwd.argtypes = [vp] * 10 + [i32, i64, i64, i32, i32, i32, i32, i32, f32,
                                                      i32, i32, i32, i32, vp, sz, vp, vp]
     p64 = C.POINTER(C.c_int64)
+    lib.spsattn_prefill_bwd_strided.restype = i32
+    lib.spsattn_prefill_bwd_strided.argtypes = [vp] * 9 + [p64, vp, i32, i64, i64, i32, i32, i32, i32, i32, f32,
+                                                           i32, i32, i32, i32, vp, sz, vp, vp]
     lib.spsattn_prefill_fwd_strided.restype = i32
     lib.spsattn_prefill_fwd_strided.argtypes = [vp, vp, vp, vp, vp, p64, p64, p64, p64, vp, i32, i64, i64,
                                                 i32, i32, i32, i32, i32, f32, i32, i32, i32, i32, vp, sz, vp, vp]

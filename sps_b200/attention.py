@@ -97,18 +97,28 @@ def prefill_attention_backward(
     if D not in _BACKWARD_HEAD_DIMS:
         raise RuntimeError(f"the backward kernels cover head_dim {_BACKWARD_HEAD_DIMS}, got {D}")
     dt = _dtype_code(q)
-    q, k, v, o, d_o = (x.contiguous() for x in (q, k, v, o, d_o.to(q.dtype)))
+    # operands are read where they lie when their rows are addressable (the token-major views of
+    # the reference's modules and the gradient autograd hands back for them); the reference copies
+    # all five (triton_sps_flash_attention.py:629-633)
+    q, k, v, o, d_o = (x if _addressable(x) else x.contiguous() for x in (q, k, v, o, d_o.to(q.dtype)))
     lse = lse.contiguous()
     assert lse.shape == (B, H, N) and lse.dtype == torch.float32
     docs, docs_ptr, docs_i64, sb, st = _docs_args(documents_idx, B, N, q.device)
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+    def grad_like(x):           # a token-major operand gets a token-major gradient
+        if x.stride(2) > x.stride(1):
+            return torch.empty((B, N, H, D), dtype=x.dtype, device=x.device).transpose(1, 2)
+        return torch.empty((B, H, N, D), dtype=x.dtype, device=x.device)
+
+    dq, dk, dv = grad_like(q), grad_like(k), grad_like(v)
+    strides = (C.c_int64 * 24)(*[s_ for t in (q, k, v, o, d_o, dq, dk, dv) for s_ in t.stride()[:3]])
     ws_bytes = lib.spsattn_prefill_bwd_workspace_bytes(B, H, N, D)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
     pw = _lib.NO_WINDOW if persistent_window is None else max(-1, min(int(persistent_window), N))
     with torch.cuda.device(q.device):
-        rc = lib.spsattn_prefill_bwd(
+        rc = lib.spsattn_prefill_bwd_strided(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
-            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), docs_ptr, docs_i64, sb, st, B, H, N, D, dt,
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), strides, docs_ptr, docs_i64, sb, st, B, H, N, D, dt,
             float(sm_scale), int(persistent_parity), max(-1, min(int(temporary_window), N)), pw,
             int(mask_flags), ws.data_ptr(), ws_bytes, _status(q.device).data_ptr(),
             torch.cuda.current_stream().cuda_stream)

@@ -35,8 +35,9 @@ constexpr int kBwdMaxThreads = 320;
 constexpr int kBwdTable = 1024;      // streamed tiles listed per block (64K rows in kDKV mode)
 
 struct BwdParams {
-  void* out0;            // kDQ: dQ, kDKV: dK   dense [B, H, N, D]
+  void* out0;            // kDQ: dQ, kDKV: dK   rows of D contiguous elements, strides below
   void* out1;            // kDKV: dV
+  int64_t out0_stride[3], out1_stride[3];       // batch, head, row (elements)
   const float* lse;      // [B, H, N], log2 domain (as written by the forward kernel)
   const float* delta;    // [B, H, N]
   const void* docs;
@@ -90,19 +91,27 @@ struct BwdCfg {
   static constexpr int kBlocksPerSM = (D == 64) ? 2 : 1;
 };
 
-// delta[b, h, i] = sum_d dO * O over dense [B*H*N, D] operands: D / 8 threads per row, 16 bytes
-// of each operand per thread
+// delta[b, h, i] = sum_d dO * O, rows addressed with each operand's own strides: D / 8 threads
+// per row, 16 bytes of each operand per thread
+struct DeltaStrides {
+  int64_t o[3], g[3];     // batch, head, row strides of O and dO (elements)
+};
 template <bool FP16, int D>
 __global__ void __launch_bounds__(256)
 bwd_delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float* __restrict__ delta,
-                 long long rows) {
+                 long long rows, int H, int N, DeltaStrides st) {
   constexpr int TPR = D / 8;                  // threads per row (8 or 16)
   const long long r = ((long long)blockIdx.x * 256 + threadIdx.x) / TPR;
   const int part = threadIdx.x % TPR;
   float acc = 0.f;
   if (r < rows) {
-    const uint4 a = reinterpret_cast<const uint4*>(o)[r * TPR + part];
-    const uint4 g = reinterpret_cast<const uint4*>(d_o)[r * TPR + part];
+    const long long bh = r / N;
+    const int i = (int)(r - bh * N);
+    const long long bb = bh / H, hh = bh - bb * H;
+    const uint4 a = reinterpret_cast<const uint4*>(
+        reinterpret_cast<const uint16_t*>(o) + bb * st.o[0] + hh * st.o[1] + (long long)i * st.o[2])[part];
+    const uint4 g = reinterpret_cast<const uint4*>(
+        reinterpret_cast<const uint16_t*>(d_o) + bb * st.g[0] + hh * st.g[1] + (long long)i * st.g[2])[part];
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
@@ -706,16 +715,20 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
       }
 
       // ---------------------------------------------------------------- epilogue
-      // the accumulations complete in order: the last one's barrier covers them all
-      if (ok && wg == 0)
-        ok = mbar_wait(bar_acc_done + 8 * ((n_tiles - 1) % Cfg::kWGs), ((n_tiles - 1) / Cfg::kWGs) & 1,
-                       abort_flag, prm.status);
-      if (ok && wg == 0) {
+      // The accumulations complete in order, so the last tile's barrier covers them all.  The
+      // warpgroup that owns the last tile writes the result: it has consumed every earlier phase
+      // of its own barrier, so this parity wait cannot be satisfied by an older phase (the other
+      // warpgroup never waited on that barrier and could pass on a stale parity).
+      const bool epilogue_wg = wg == (n_tiles - 1) % Cfg::kWGs;
+      if (ok && epilogue_wg)
+        ok = mbar_wait(bar_acc_done + 8 * wg, ((n_tiles - 1) / Cfg::kWGs) & 1, abort_flag, prm.status);
+      if (ok && epilogue_wg) {
         tc_fence_after();
-        const size_t row_off = ((size_t)bh * prm.N + (size_t)my_row) * D * 2;
 #pragma unroll
         for (int a = 0; a < (kDKV ? 2 : 1); ++a) {
-          uint8_t* o_row = reinterpret_cast<uint8_t*>(a == 0 ? prm.out0 : prm.out1) + row_off;
+          const int64_t* os = a == 0 ? prm.out0_stride : prm.out1_stride;
+          uint8_t* o_row = reinterpret_cast<uint8_t*>(a == 0 ? prm.out0 : prm.out1) +
+                           (b * os[0] + h * os[1] + (int64_t)my_row * os[2]) * 2;
 #pragma unroll
           for (int q4 = 0; q4 < D / 32; ++q4) {
             uint32_t r[32];
@@ -742,9 +755,10 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
     const int my_row = kDKV ? ks * (x0 + tid) + stream : x0 + tid;
     const bool my_valid = kDKV ? (x0 + tid < Tk) : (my_row < prm.N);
     if (my_valid) {
-      const size_t row_off = ((size_t)bh * prm.N + (size_t)my_row) * D * 2;
       for (int a = 0; a < (kDKV ? 2 : 1); ++a) {
-        uint4* o_row = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a == 0 ? prm.out0 : prm.out1) + row_off);
+        const int64_t* os = a == 0 ? prm.out0_stride : prm.out1_stride;
+        uint4* o_row = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a == 0 ? prm.out0 : prm.out1) +
+                                                (b * os[0] + h * os[1] + (int64_t)my_row * os[2]) * 2);
         for (int e = 0; e < D / 8; ++e) o_row[e] = make_uint4(0, 0, 0, 0);
       }
     }

@@ -422,13 +422,14 @@ size_t spsattn_prefill_bwd_workspace_bytes(int B, int H, int N, int D) {
          align_up((size_t)B * N * sizeof(int), 256);
 }
 
-int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                        const float* lse, void* dq, void* dk, void* dv, const void* doc_ids,
-                        int doc_is_i64, int64_t doc_stride_b, int64_t doc_stride_t, int B, int H, int N,
-                        int D, int dtype, float sm_scale, int persistent_parity, int temporary_window,
-                        int persistent_window, int mask_flags, void* workspace, size_t workspace_bytes,
-                        int* device_status, void* stream) {
-  if (!q || !k || !v || !o || !d_o || !lse || !dq || !dk || !dv) return SPSATTN_ERR_ARG;
+int spsattn_prefill_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                const float* lse, void* dq, void* dk, void* dv, const int64_t* strides,
+                                const void* doc_ids, int doc_is_i64, int64_t doc_stride_b,
+                                int64_t doc_stride_t, int B, int H, int N, int D, int dtype, float sm_scale,
+                                int persistent_parity, int temporary_window, int persistent_window,
+                                int mask_flags, void* workspace, size_t workspace_bytes,
+                                int* device_status, void* stream) {
+  if (!q || !k || !v || !o || !d_o || !lse || !dq || !dk || !dv || !strides) return SPSATTN_ERR_ARG;
   if (B <= 0 || H <= 0 || N <= 0) return SPSATTN_ERR_ARG;
   if (dtype != SPSATTN_DTYPE_BF16 && dtype != SPSATTN_DTYPE_FP16) return SPSATTN_ERR_ARG;
   if (persistent_parity != SPSATTN_PARITY_EVEN && persistent_parity != SPSATTN_PARITY_ODD &&
@@ -445,6 +446,13 @@ int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void*
   if (workspace == nullptr || workspace_bytes < spsattn_prefill_bwd_workspace_bytes(B, H, N, D))
     return SPSATTN_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return SPSATTN_ERR_ALIGN;
+  // strides: eight (batch, head, row) triples in elements, in the order q, k, v, o, d_o, dq, dk, dv
+  Strides sx[8];
+  for (int x = 0; x < 8; ++x) {
+    sx[x] = {strides[3 * x], strides[3 * x + 1], strides[3 * x + 2]};
+    if (!strides_ok(sx[x], D)) return SPSATTN_ERR_ALIGN;
+  }
+  const Strides &sq = sx[0], &sk = sx[1], &sv = sx[2], &so = sx[3], &sg = sx[4];
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool fp16 = dtype == SPSATTN_DTYPE_FP16;
 
@@ -462,24 +470,24 @@ int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void*
   }
   const long long rows = (long long)B * H * N;
   const unsigned dgrid = (unsigned)((rows * (D / 8) + 255) / 256);
+  const DeltaStrides ds = {{so.b, so.h, so.n}, {sg.b, sg.h, sg.n}};
   if (D == 64) {
-    if (fp16) bwd_delta_kernel<true, 64><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows);
-    else bwd_delta_kernel<false, 64><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows);
+    if (fp16) bwd_delta_kernel<true, 64><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows, H, N, ds);
+    else bwd_delta_kernel<false, 64><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows, H, N, ds);
   } else {
-    if (fp16) bwd_delta_kernel<true, 128><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows);
-    else bwd_delta_kernel<false, 128><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows);
+    if (fp16) bwd_delta_kernel<true, 128><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows, H, N, ds);
+    else bwd_delta_kernel<false, 128><<<dgrid, 256, 0, st>>>(o, d_o, delta, rows, H, N, ds);
   }
   if ((rc = (int)cudaGetLastError()) != 0) return rc;
 
   const MaskParams mask = make_mask(N, persistent_parity, temporary_window, persistent_window, mask_flags);
-  const Strides dense = {(int64_t)H * N * D, (int64_t)N * D, (int64_t)D};
   CUtensorMap q128, do128, q64, do64, ks_map, vs_map;
-  if ((rc = encode_q_map(&q128, q, B, H, N, D, dense, dtype, 128)) != 0) return rc;
-  if ((rc = encode_q_map(&do128, d_o, B, H, N, D, dense, dtype, 128)) != 0) return rc;
-  if ((rc = encode_q_map(&q64, q, B, H, N, D, dense, dtype, 64)) != 0) return rc;
-  if ((rc = encode_q_map(&do64, d_o, B, H, N, D, dense, dtype, 64)) != 0) return rc;
-  if ((rc = encode_kv_map(&ks_map, k, B, H, N, D, mask.ks, dense, dtype)) != 0) return rc;
-  if ((rc = encode_kv_map(&vs_map, v, B, H, N, D, mask.ks, dense, dtype)) != 0) return rc;
+  if ((rc = encode_q_map(&q128, q, B, H, N, D, sq, dtype, 128)) != 0) return rc;
+  if ((rc = encode_q_map(&do128, d_o, B, H, N, D, sg, dtype, 128)) != 0) return rc;
+  if ((rc = encode_q_map(&q64, q, B, H, N, D, sq, dtype, 64)) != 0) return rc;
+  if ((rc = encode_q_map(&do64, d_o, B, H, N, D, sg, dtype, 64)) != 0) return rc;
+  if ((rc = encode_kv_map(&ks_map, k, B, H, N, D, mask.ks, sk, dtype)) != 0) return rc;
+  if ((rc = encode_kv_map(&vs_map, v, B, H, N, D, mask.ks, sv, dtype)) != 0) return rc;
 
   BwdParams prm;
   memset(&prm, 0, sizeof(prm));
@@ -501,8 +509,13 @@ int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void*
   prm.status = device_status;
 
   // dK, dV: one block per 128-token key tile of each parity stream
-  prm.out0 = dk;
-  prm.out1 = dv;
+  auto set_out = [&](int slot, void* ptr, const Strides& s3) {
+    (slot == 0 ? prm.out0 : prm.out1) = ptr;
+    int64_t* dst = slot == 0 ? prm.out0_stride : prm.out1_stride;
+    dst[0] = s3.b, dst[1] = s3.h, dst[2] = s3.n;
+  };
+  set_out(0, dk, sx[6]);
+  set_out(1, dv, sx[7]);
   prm.n_xtiles = mask.ks * ((N / mask.ks + 127) / 128);
   if (D == 64)
     rc = fp16 ? launch_prefill_bwd<64, true, kBwdDKV>(ks_map, vs_map, q64, do64, prm, st)
@@ -512,7 +525,7 @@ int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void*
               : launch_prefill_bwd<128, false, kBwdDKV>(ks_map, vs_map, q64, do64, prm, st);
   if (rc != 0) return rc;
   // dQ: one block per 128-row query tile
-  prm.out0 = dq;
+  set_out(0, dq, sx[5]);
   prm.out1 = nullptr;
   prm.n_xtiles = (N + 127) / 128;
   if (D == 64)
@@ -520,6 +533,24 @@ int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void*
                 : launch_prefill_bwd<64, false, kBwdDQ>(q128, do128, ks_map, vs_map, prm, st);
   return fp16 ? launch_prefill_bwd<128, true, kBwdDQ>(q128, do128, ks_map, vs_map, prm, st)
               : launch_prefill_bwd<128, false, kBwdDQ>(q128, do128, ks_map, vs_map, prm, st);
+}
+
+int spsattn_prefill_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                        const float* lse, void* dq, void* dk, void* dv, const void* doc_ids,
+                        int doc_is_i64, int64_t doc_stride_b, int64_t doc_stride_t, int B, int H, int N,
+                        int D, int dtype, float sm_scale, int persistent_parity, int temporary_window,
+                        int persistent_window, int mask_flags, void* workspace, size_t workspace_bytes,
+                        int* device_status, void* stream) {
+  int64_t dense[24];
+  for (int x = 0; x < 8; ++x) {
+    dense[3 * x] = (int64_t)H * N * D;
+    dense[3 * x + 1] = (int64_t)N * D;
+    dense[3 * x + 2] = D;
+  }
+  return spsattn_prefill_bwd_strided(q, k, v, o, d_o, lse, dq, dk, dv, dense, doc_ids, doc_is_i64,
+                                     doc_stride_b, doc_stride_t, B, H, N, D, dtype, sm_scale,
+                                     persistent_parity, temporary_window, persistent_window, mask_flags,
+                                     workspace, workspace_bytes, device_status, stream);
 }
 
 int spsattn_prefill_fwd(const void* q, const void* k, const void* v, void* o, float* lse,

@@ -178,6 +178,61 @@ def test_backward_is_linear_in_the_output_gradient():
     sps_b200.check_device_status(dev)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+def test_backward_reads_and_writes_token_major_views_in_place(d):
+    """The layouts the reference's modules produce (sps/core.py:45-55): q, k, v as transposed views
+    of a fused [B, N, 3*H*D] projection, dO as the transposed view autograd hands back.  Same
+    gradients as the dense call, bit for bit, and the q / k / v gradients come back token-major."""
+    import sps_b200
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(3 + d)
+    B, H, N, w = 2, 2, 640, 24
+    qkv = torch.randn(B, N, 3 * H * d, generator=gen).bfloat16().to(dev)
+    docs = _packed_docs(B, N // 2, 90, 4).to(dev)
+    views = [t.view(B, N, H, d).transpose(1, 2) for t in qkv.split(H * d, dim=2)]
+    g_tm = torch.randn(B, N, H, d, generator=gen).bfloat16().to(dev).transpose(1, 2)
+    scale = 1.0 / math.sqrt(d)
+    o, lse = sps_b200.prefill_attention(*views, scale, persistent_parity=0, temporary_window=w,
+                                        documents_idx=docs, return_lse=True)
+    bw = sps_b200.attention.prefill_attention_backward
+    got = bw(*views, o, lse, g_tm, scale, persistent_parity=0, temporary_window=w, documents_idx=docs)
+    dense = [t.contiguous() for t in views]
+    want = bw(*dense, o.contiguous(), lse, g_tm.contiguous(), scale, persistent_parity=0, temporary_window=w,
+              documents_idx=docs)
+    for x, y in zip(got, want):
+        assert x.stride(2) > x.stride(1)                 # token-major
+        assert torch.equal(x, y)
+    # and through autograd down to the fused projection
+    leaf = qkv.clone().requires_grad_(True)
+    lv = [t.view(B, N, H, d).transpose(1, 2) for t in leaf.split(H * d, dim=2)]
+    out = sps_b200.sps_sliding_attention(*lv, scale, w, documents_idx_BxT=docs)
+    out.transpose(1, 2).reshape(B, N, H * d).backward(g_tm.transpose(1, 2).reshape(B, N, H * d))
+    ref = torch.cat([t.transpose(1, 2).reshape(B, N, H * d) for t in want], dim=2)
+    assert torch.equal(leaf.grad, ref)
+    sps_b200.check_device_status(dev)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_backward_is_deterministic_for_every_tile_count(d):
+    """No atomics anywhere: repeated calls give identical bits.  Lengths chosen so that the number
+    of streamed tiles per block takes every residue modulo 4 (at head_dim 128 two warpgroups take
+    alternate tiles and the one that owns the last tile writes the result)."""
+    import sps_b200
+    dev = torch.device("cuda:0")
+    bw = sps_b200.attention.prefill_attention_backward
+    for n in (128, 192, 320, 448, 684, 1100):
+        gen = torch.Generator().manual_seed(n)
+        q, k, v, g = (torch.randn(1, 2, n, d, generator=gen).bfloat16().to(dev) for _ in range(4))
+        scale = 1.0 / math.sqrt(d)
+        o, lse = sps_b200.prefill_attention(q, k, v, scale, persistent_parity=1, temporary_window=200, return_lse=True)
+        first = bw(q, k, v, o, lse, g, scale, persistent_parity=1, temporary_window=200)
+        for _ in range(6):
+            again = bw(q, k, v, o, lse, g, scale, persistent_parity=1, temporary_window=200)
+            for x, y in zip(first, again):
+                assert torch.equal(x, y), (n, d)
+    sps_b200.check_device_status(dev)
+
+
 def test_backward_needs_a_supported_head_dim():
     import sps_b200
     dev = torch.device("cuda:0")
