@@ -510,10 +510,12 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         l_run += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         if (tid == 0) SPS_TRACE(j, 4);
 
-        // the shared-memory P tile is free, and O may be rescaled, once the previous P V product is
-        // done; P in tensor memory needs no wait (the S this thread read was written after the
-        // last product that read these columns, in issue order)
-        if (j > 0 && (!Cfg::kPTmem || rescale)) {
+        // The shared-memory P tile is free, and O may be rescaled, once the previous P V product is
+        // done.  P in tensor memory may be written before that (the S this thread read was written
+        // after the last product that read these columns, in issue order), so there the wait comes
+        // after the P write; it is still made for every tile: a parity wait is only meaningful for
+        // a waiter that has consumed every earlier phase of the barrier.
+        if (!Cfg::kPTmem && j > 0) {
           if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag, prm.status)) {
             ok = false;
             break;
@@ -536,6 +538,13 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                        : "memory");
         }
         if (tid == 0) SPS_TRACE(j, 6);
+        if (Cfg::kPTmem && j > 0) {
+          if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag, prm.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+        }
         if (j > 0 && rescale) {
 #pragma unroll
           for (int q4 = 0; q4 < D / 32; ++q4) {
