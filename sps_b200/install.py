@@ -4,7 +4,10 @@ The reference reaches its attention kernels through plain module attributes
 (src/modeling/models/sps/core.py:68, reverse_sps/core.py:85, full_attention_model.py:110 and
 :550, reverse_sps/inference.py:312, :354, :206); ``install()`` points each of them at the
 function of the same signature in this package.  It needs the reference's ``modeling`` package
-on ``sys.path`` and does nothing else to it.
+on ``sys.path`` and does nothing else to it.  The three prefill functions are autograd functions
+(head_dim 64 and 128), so a model bound this way trains through them as it does through the
+reference's (triton_sps_flash_attention.py:491-720); the decode functions are for generation
+and refuse inputs that require grad.
 """
 
 from __future__ import annotations
