@@ -449,7 +449,8 @@ def run_case(args):
     """Small single-kernel cases for profiler captures (a few hundred MB on the device, inputs
     still larger than L2): `prefill-small` = 4 of the 8 batch rows of the s-scale prefill,
     `full-window-small` = 4 of the 16 heads of the full-window prefill (head_dim 128),
-    `backward-small` = the backward of those 4 rows, `decode-small` = 32 of the 128 decode sequences, `generation-small` / `generation` = the
+    `backward-small` = the backward of those 4 rows, `backward-full-window-small` = the backward
+    of the 4-head full-window case, `decode-small` = 32 of the 128 decode sequences, `generation-small` / `generation` = the
     whole-model generation leg alone on a tiny / the full model.  Prints a short JSON line, not
     the benchmark contract line."""
     import sps_b200
@@ -474,8 +475,11 @@ def run_case(args):
         fn = lambda: sps_b200.prefill_attention(wl.q, wl.k, wl.v, wl.sm_scale, persistent_parity=0,
                                                 temporary_window=wl.window, documents_idx=None, out=out)
         work, unit = wl.flops / 1e12, "TFLOP/s"
-    elif args.case == "backward-small":
-        wl = workloads.make_prefill(PREFILL, device, batch_slice=slice(0, 4))
+    elif args.case in ("backward-small", "backward-full-window-small"):
+        if args.case == "backward-small":
+            wl = workloads.make_prefill(PREFILL, device, batch_slice=slice(0, 4))
+        else:
+            wl = workloads.make_prefill(PREFILL_FULL_WINDOW, device, head_slice=slice(0, 4))
         o_b, lse_b = sps_b200.prefill_attention(wl.q, wl.k, wl.v, wl.sm_scale, persistent_parity=0,
                                                 temporary_window=wl.window, documents_idx=wl.docs,
                                                 return_lse=True)
@@ -581,7 +585,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--case", choices=["full", "prefill-small", "full-window-small", "backward-small", "decode-small", "generation-small", "generation"], default="full")
+    ap.add_argument("--case", choices=["full", "prefill-small", "full-window-small", "backward-small", "backward-full-window-small", "decode-small", "generation-small", "generation"], default="full")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-decode", action="store_true")
     ap.add_argument("--skip-backward", action="store_true", help="skip the prefill backward section")
