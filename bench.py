@@ -53,56 +53,88 @@ def load_peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
+_SAMPLER_SRC = r"""
+import sys, time
+idx, period = int(sys.argv[1]), float(sys.argv[2])
+try:
+    import pynvml as nv
+    nv.nvmlInit()
+    h = nv.nvmlDeviceGetHandleByIndex(idx)
+    print("MAX %d" % nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM), flush=True)
+except Exception as e:
+    print("ERR %r" % (e,), flush=True)
+    sys.exit(0)
+while True:
+    try:
+        c = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+        r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+        sys.stdout.write("%.6f %d %d\\n" % (time.time(), c, r))
+        sys.stdout.flush()
+    except Exception:
+        pass
+    time.sleep(period)
+"""
+
+
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """SM clock and throttle reasons through NVML while the timed regions run.  The polling
+    loop lives in a child process, so it never competes with the launching thread for the
+    interpreter; the parent only notes the wall-clock window of every timed region and keeps the
+    samples that fall inside one.  Reading clocks changes no setting of the GPU."""
 
-    def __init__(self, index: int, period_s: float = 0.004):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thread = None
+    _BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        import subprocess
+        import tempfile
+        self.windows, self.max_mhz = [], None
+        self._out = tempfile.NamedTemporaryFile(mode="w+", suffix=".clk", delete=False)
         try:
-            import pynvml
-            pynvml.nvmlInit()
-            self._nv = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_SRC, str(index), str(period_s)],
+                                          stdout=self._out, stderr=subprocess.DEVNULL)
         except Exception:
-            self._nv = None
-        self._period = period_s
+            self._proc = None
+        t0 = time.time()
+        while self._proc is not None and time.time() - t0 < 5.0:        # wait for the first line
+            with open(self._out.name) as f:
+                head = f.readline()
+            if head.startswith("MAX"):
+                self.max_mhz = float(head.split()[1])
+                break
+            if head.startswith("ERR") or self._proc.poll() is not None:
+                break
+            time.sleep(0.02)
 
-    def _loop(self):
-        nv = self._nv
-        names = {
-            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
-            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
-            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
-            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
-        }
-        while not self._stop.is_set():
-            try:
-                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
-                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
-                for bit, name in names.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
-            time.sleep(self._period)
+    def begin(self):
+        self._t0 = time.time()
 
-    def __enter__(self):
-        if self._nv is not None:
-            self._thread = threading.Thread(target=self._loop, daemon=True)
-            self._thread.start()
-        return self
-
-    def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
+    def end(self):
+        self.windows.append((self._t0, time.time()))
 
     def summary(self):
-        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None,
-                "sm_max_mhz": self.max_mhz, "samples": len(self.samples), "reasons": sorted(self.reasons)}
+        if self._proc is not None:
+            self._proc.terminate()          # our own child, by handle
+            try:
+                self._proc.wait(timeout=5)
+            except Exception:
+                pass
+        samples, reasons = [], set()
+        try:
+            with open(self._out.name) as f:
+                for line in f:
+                    parts = line.split()
+                    if len(parts) != 3 or parts[0] in ("MAX", "ERR"):
+                        continue
+                    t, c, r = float(parts[0]), float(parts[1]), int(parts[2])
+                    if any(a <= t <= b for a, b in self.windows):
+                        samples.append(c)
+                        reasons.update(name for bit, name in self._BITS.items() if r & bit)
+            os.unlink(self._out.name)
+        except Exception:
+            pass
+        return {"sm_mhz": float(np.median(samples)) if samples else None, "sm_max_mhz": self.max_mhz,
+                "samples": len(samples), "reasons": sorted(reasons),
+                "how": "NVML polled every 2 ms by a child process; samples inside the timed regions only"}
 
 
 def dist_setup(n_gpus: int):
@@ -131,26 +163,48 @@ def max_over_ranks(x: float, world: int, device) -> float:
     return float(t.item())
 
 
-def timed_steps(fn, steps, warmup, world, device):
-    """W untimed steps, then exactly K steps bracketed by barrier + synchronize; CUDA events on
-    the launching stream give the whole region and every launch.  Returns (region ms as max over
-    ranks, mean launch ms on this rank)."""
+def gather_over_ranks(x: float, world: int, device) -> list:
+    if world == 1:
+        return [x]
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    out = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return [float(o.item()) for o in out]
+
+
+def timed_steps(fn, steps, warmup, world, device, regions=5, sampler=None):
+    """W untimed steps, then `regions` back-to-back timed regions of exactly K steps, each
+    bracketed by barrier + synchronize on both sides and timed with CUDA events on the launching
+    stream.  The region reported is the median one (by its max over ranks): a single late rank
+    in a region of a few milliseconds otherwise decides the figure.  Returns (region ms as max
+    over ranks, mean launch ms on this rank, details)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    barrier(world)
-    torch.cuda.synchronize()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
-    ev[0].record()
-    for i in range(steps):
-        fn()
-        ev[i + 1].record()
-    torch.cuda.synchronize()
-    barrier(world)
-    torch.cuda.synchronize()
-    region = ev[0].elapsed_time(ev[-1])
-    per = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
-    return max_over_ranks(region, world, device), float(np.mean(per))
+    mine, per_launch = [], []
+    for _ in range(regions):
+        barrier(world)
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        if sampler is not None:
+            sampler.begin()
+        ev[0].record()
+        for i in range(steps):
+            fn()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        if sampler is not None:
+            sampler.end()
+        barrier(world)
+        torch.cuda.synchronize()
+        mine.append(ev[0].elapsed_time(ev[-1]))
+        per_launch.append(float(np.mean([ev[i].elapsed_time(ev[i + 1]) for i in range(steps)])))
+    maxima = [max_over_ranks(m, world, device) for m in mine]
+    pick = int(np.argsort(maxima)[len(maxima) // 2])
+    details = {"regions_ms_max_over_ranks": maxima, "reported_region": pick,
+               "rank_region_ms": gather_over_ranks(mine[pick], world, device)}
+    return maxima[pick], per_launch[pick], details
 
 
 # ------------------------------------------------------------------------------------- ours

@@ -285,6 +285,23 @@ int spsattn_decode_step(const void* q, int nq, void* out, int out_dtype,
  * segment) or SPSATTN_ERR_ARG.  Process-wide. */
 int spsattn_debug_decode_path(int path);
 
+/* Test hook: which tensor-core prefill kernel serves head_dim 64.  0 = automatic (today the
+ * 64-key-tile kernel with P through shared memory, three blocks per SM, which also serves
+ * head_dim 128 and measures faster), 1 = that kernel, forced, 2 = the persistent kernel with
+ * 128-key tiles, P kept in tensor memory and a hand-pipelined softmax (two blocks per SM drawing
+ * work items from a counter).  All apply the same plan and the same visibility rule and are held
+ * to the same parity tests.  Process-wide.  No counterpart in the reference. */
+int spsattn_debug_prefill_path(int path);
+
+/* Test hook for the bounded waits of the kernels: launches one warp that waits on a barrier
+ * nobody arrives at (no copy or tensor-core operation in flight), with a limit of `limit_ns`
+ * nanoseconds (at most 1e9).  The wait gives up, writes SPSATTN_STATUS_WAIT_EXPIRED to
+ * *device_status as the attention kernels do, sets device_result[0] = 1 (when given) and the
+ * block ends normally.  While the status word is non-zero the tensor-core attention kernels
+ * return without computing; the caller clears it.  No counterpart in the reference. */
+int spsattn_debug_wait_expiry(int* device_status, unsigned long long limit_ns, int* device_result,
+                              void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Decode KV-cache update, in place (decode_attention_fast.py:34-136): for every active sequence
  * insert k_window/v_window into the ring [S,H,window_storage,D] at `pos` when the ring is full

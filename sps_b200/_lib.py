@@ -24,7 +24,7 @@ EXPORTS = (
     "spsattn_decode_workspace_bytes", "spsattn_decode_fwd", "spsattn_decode_fwd_noalloc",
     "spsattn_kv_update", "spsattn_fill_decode_caches", "spsattn_rope_cast", "spsattn_debug_visibility",
     "spsattn_decode_step_workspace_bytes", "spsattn_decode_step", "spsattn_qkv_rope_cast",
-    "spsattn_add_rmsnorm", "spsattn_swiglu", "spsattn_debug_decode_path",
+    "spsattn_add_rmsnorm", "spsattn_swiglu", "spsattn_debug_decode_path", "spsattn_debug_prefill_path", "spsattn_debug_wait_expiry",
     "spsattn_prefill_bwd_workspace_bytes", "spsattn_prefill_bwd", "spsattn_prefill_bwd_strided",
 )
 
@@ -131,6 +131,10 @@ def load() -> C.CDLL:
     lib.spsattn_swiglu.argtypes = [vp, vp, i32, C.c_longlong, i32, vp]
     lib.spsattn_debug_decode_path.restype = i32
     lib.spsattn_debug_decode_path.argtypes = [i32]
+    lib.spsattn_debug_wait_expiry.restype = i32
+    lib.spsattn_debug_wait_expiry.argtypes = [vp, C.c_ulonglong, vp, vp]
+    lib.spsattn_debug_prefill_path.restype = i32
+    lib.spsattn_debug_prefill_path.argtypes = [i32]
     lib.spsattn_debug_visibility.restype = i32
     lib.spsattn_debug_visibility.argtypes = [vp, vp, i32, i64, i64, i32, i32, i32, i32, i32, i32, vp, sz, vp]
     _lib = lib

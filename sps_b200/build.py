@@ -16,7 +16,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libspsattn.so")
 SOURCES = ["spsattn_api.cu"]
-HEADERS = ["common.cuh", "mask.cuh", "prefill_sm100.cuh", "prefill_bwd_sm100.cuh", "prefill_aux.cuh", "decode.cuh", "decode_sm100.cuh",
+HEADERS = ["common.cuh", "mask.cuh", "prefill_sm100.cuh", "prefill_wide_sm100.cuh", "prefill_bwd_sm100.cuh", "prefill_aux.cuh", "decode.cuh", "decode_sm100.cuh",
            "kv_update.cuh", "model_glue.cuh", "rope.cuh", "cache_fill.cuh", os.path.join("..", "..", "include", "spsattn.h")]
 
 

@@ -17,7 +17,7 @@ __device__ __forceinline__ long long load_doc(const void* docs, int is_i64, size
 // Each thread scans kItems consecutive rows, so rows up to 8192 need a single pass.
 __global__ void __launch_bounds__(1024)
 doc_prepass_kernel(const void* docs, int is_i64, int64_t stride_b, int64_t stride_t, int N,
-                   int* __restrict__ lo, int* __restrict__ mono) {
+                   int* __restrict__ lo, int* __restrict__ mono, int* __restrict__ work_counter) {
   constexpr int kItems = 8;
   __shared__ int s_warp[32];
   __shared__ int s_carry;
@@ -30,6 +30,8 @@ doc_prepass_kernel(const void* docs, int is_i64, int64_t stride_b, int64_t strid
   if (tid == 0) {
     s_carry = 0;
     s_mono = 1;
+    // the attention kernel that follows in the stream draws its work items from this counter
+    if (b == 0 && work_counter != nullptr) *work_counter = 0;
   }
   __syncthreads();
   bool dec = false;
@@ -83,6 +85,27 @@ doc_prepass_kernel(const void* docs, int is_i64, int64_t stride_b, int64_t strid
   if (dec) s_mono = 0;
   __syncthreads();
   if (tid == 0) mono[b] = s_mono;
+}
+
+// Test hook for the bounded waits: one warp waits, with the given limit, on an mbarrier that
+// nobody ever arrives at.  No copy or tensor-core operation is in flight; the wait gives up,
+// reports SPSATTN_STATUS_WAIT_EXPIRED through the status word exactly as the attention kernels
+// do, and the block ends normally.  result[0] = 1 when the wait returned "gave up".
+__global__ void __launch_bounds__(32)
+wait_expiry_kernel(int* status, unsigned long long limit_ns, int* result) {
+  __shared__ __align__(8) unsigned long long s_bar;
+  __shared__ int s_abort;
+  const uint32_t bar = smem_u32(&s_bar);
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(bar, 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+  bool ok = mbar_try_wait(bar, 0);
+  if (!ok) ok = mbar_wait_slow(bar, 0, &s_abort, status, limit_ns);
+  ok = __all_sync(0xffffffffu, ok);
+  if (threadIdx.x == 0 && result != nullptr) result[0] = ok ? 0 : 1;
 }
 
 // vis[b][i][j] = 1 iff key row j is visible to query row i, using the kernels' own arithmetic.

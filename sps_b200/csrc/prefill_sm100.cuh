@@ -39,6 +39,8 @@ struct PrefillParams {
   MaskParams mask;
   float scale_log2;      // sm_scale * log2(e)
   int* status;
+  int* work_counter;     // persistent kernels: next work item (zero at launch), or null
+  int group_heads;       // persistent kernels: (batch, head) pairs whose K/V share L2 at a time
   long long* trace;      // cycle stamps (only read by builds with -DSPSATTN_TRACE), else null
 };
 
@@ -101,6 +103,8 @@ struct BlockPlan {
   int general_docs;  // ids are not monotone: compare ids element by element
 };
 
+// TN = key tokens per tile (the plan's streams must have been made with the same tile size)
+template <int TN = kTileN>
 __device__ __forceinline__ TileInfo tile_info(const BlockPlan& bp, int j) {
   TileInfo t;
   int s = 0;
@@ -109,9 +113,9 @@ __device__ __forceinline__ TileInfo tile_info(const BlockPlan& bp, int j) {
     s = 1;
   }
   t.stream = bp.stream_id[s];
-  t.k0 = bp.sp[s].top - (kTileN - 1) - kTileN * j;
+  t.k0 = bp.sp[s].top - (TN - 1) - TN * j;
   t.masked = bp.sp[s].force_mask || bp.general_docs ||
-             !(bp.sp[s].kmin_hi <= t.k0 && bp.sp[s].kmax_lo >= t.k0 + kTileN - 1);
+             !(bp.sp[s].kmin_hi <= t.k0 && bp.sp[s].kmax_lo >= t.k0 + TN - 1);
   return t;
 }
 
@@ -130,8 +134,9 @@ __device__ __forceinline__ TileInfo unpack_tile(int w) {
   t.masked = (w & 1) != 0;
   return t;
 }
+template <int TN = kTileN>
 __device__ __forceinline__ TileInfo get_tile(const BlockPlan& bp, const int* table, int j) {
-  return j < kTileTable ? unpack_tile(table[j]) : tile_info(bp, j);
+  return j < kTileTable ? unpack_tile(table[j]) : tile_info<TN>(bp, j);
 }
 
 constexpr float kRescaleLog2 = 8.0f;
@@ -152,9 +157,15 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int lane = tid & 31;
   if (tid == 0) SPS_TRACE(0, 15);
 
-  // heavy query tiles (late rows) first, all tiles of one (b,h) adjacent so K/V stay in L2
-  const int bh = blockIdx.x / prm.n_qtiles;
-  const int qt = prm.n_qtiles - 1 - (blockIdx.x % prm.n_qtiles);
+  // (batch, head) pairs go in groups whose K/V fit L2 together; inside a group the late (heavy)
+  // query tiles of all its heads come first, so the launch ends on light blocks
+  const int gh = prm.group_heads > 0 ? prm.group_heads : 1;
+  const int per_group = gh * prm.n_qtiles;
+  const int grp = blockIdx.x / per_group;
+  const int in_grp = blockIdx.x - grp * per_group;
+  const int gsize = min(gh, prm.B * prm.H - grp * gh);
+  const int bh = grp * gh + in_grp % gsize;
+  const int qt = prm.n_qtiles - 1 - in_grp / gsize;
   const int b = bh / prm.H;
   const int h = bh - b * prm.H;
   const int i0 = qt * kTileM;
@@ -496,6 +507,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_mc, neg_mc);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
         uint32_t pk[kTileN / 2];
+#ifdef SPSATTN_EXP_PAIRWISE
 #pragma unroll
         for (int e = 0; e < kTileN; e += 4) {
           const float2 xa = __ffma2_rn(make_float2(s[e], s[e + 1]), c2, nm2);
@@ -507,6 +519,35 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           pk[e / 2] = pack2<FP16>(pa.x, pa.y);
           pk[e / 2 + 1] = pack2<FP16>(pb.x, pb.y);
         }
+#else
+        // Written as a software pipeline: all exponents first, then the exponentials in groups
+        // of eight issued back to back (their order is pinned), each group followed by the row
+        // sum and the packing of the group before it.  No add or pack then waits for an
+        // exponential that was asked for an instruction earlier, and the special-function unit
+        // is fed without gaps.
+#pragma unroll
+        for (int e = 0; e < kTileN; e += 2) {
+          const float2 xv = __ffma2_rn(make_float2(s[e], s[e + 1]), c2, nm2);
+          s[e] = xv.x;
+          s[e + 1] = xv.y;
+        }
+#pragma unroll
+        for (int grp = 0; grp <= kTileN / 8; ++grp) {
+          if (grp < kTileN / 8) {
+#pragma unroll
+            for (int e = grp * 8; e < grp * 8 + 8; ++e) s[e] = ex2_ordered(s[e]);
+          }
+          if (grp > 0) {
+#pragma unroll
+            for (int e = (grp - 1) * 8; e < grp * 8; e += 4) {
+              sum_a = __fadd2_rn(sum_a, make_float2(s[e], s[e + 1]));
+              sum_b = __fadd2_rn(sum_b, make_float2(s[e + 2], s[e + 3]));
+              pk[e / 2] = pack2<FP16>(s[e], s[e + 1]);
+              pk[e / 2 + 1] = pack2<FP16>(s[e + 2], s[e + 3]);
+            }
+          }
+        }
+#endif
         l_run += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         if (tid == 0) SPS_TRACE(j, 4);
 

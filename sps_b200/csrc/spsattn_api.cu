@@ -17,6 +17,7 @@
 #include "model_glue.cuh"
 #include "prefill_aux.cuh"
 #include "prefill_sm100.cuh"
+#include "prefill_wide_sm100.cuh"
 #include "prefill_bwd_sm100.cuh"
 #include "rope.cuh"
 
@@ -52,8 +53,9 @@ inline int clamp_window(long long w, int n) {
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-// workspace layout of the prefill pre-pass: [mono: B ints, padded to 256 B][lo: B*N ints]
-size_t prefill_ws_mono_bytes(int B) { return align_up((size_t)B * sizeof(int), 256); }
+// workspace layout of the prefill pre-pass: [mono: B ints, work counter: 1 int, padded to 256 B]
+// [lo: B*N ints]
+size_t prefill_ws_mono_bytes(int B) { return align_up((size_t)(B + 1) * sizeof(int), 256); }
 
 MaskParams make_mask(int N, int parity, int w, int pw, int flags) {
   MaskParams m;
@@ -94,13 +96,13 @@ int encode_q_map(CUtensorMap* tm, const void* ptr, int B, int H, int N, int D, S
 // other parity are skipped by the stride, out-of-range tokens read as zero and the next head
 // is never touched.
 int encode_kv_map(CUtensorMap* tm, const void* ptr, int B, int H, int N, int D, int ks, Strides st,
-                  int dtype) {
+                  int dtype, int box_tokens = kTileN) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return SPSATTN_ERR_DRIVER;
   cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)ks, (cuuint64_t)(N / ks), (cuuint64_t)H, (cuuint64_t)B};
   cuuint64_t strides[4] = {(cuuint64_t)st.n * 2, (cuuint64_t)ks * st.n * 2, (cuuint64_t)st.h * 2,
                            (cuuint64_t)st.b * 2};
-  cuuint32_t box[5] = {64, 1, (cuuint32_t)kTileN, 1, 1};
+  cuuint32_t box[5] = {64, 1, (cuuint32_t)box_tokens, 1, 1};
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUresult r = enc(tm, dtype == SPSATTN_DTYPE_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
@@ -131,6 +133,38 @@ int launch_prefill_sm100(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   return (int)cudaGetLastError();
 }
 
+// Persistent launch: two blocks per SM draw the (batch, head, query tile) items from
+// prm.work_counter (zero at launch), or take them with a fixed stride when there is no counter.
+template <bool FP16>
+int launch_prefill_wide(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                        const PrefillParams& prm, cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(prefill_wide_sm100_kernel<FP16>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, WideCfg::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return (int)attr_err;
+  const long long items = (long long)prm.n_qtiles * prm.B * prm.H;
+  if (items <= 0 || items > 0x7fffffffLL) return SPSATTN_ERR_TOO_LARGE;
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return (int)e;
+#ifdef SPSATTN_ONE_CTA
+  const long long per_sm = 1;      // tuning builds: one block per SM
+#else
+  const long long per_sm = 2;
+#endif
+  const long long blocks = items < per_sm * sms ? items : per_sm * sms;
+  prefill_wide_sm100_kernel<FP16><<<(unsigned)blocks, kWideThreads, WideCfg::kSmemBytes, st>>>(tq, tk, tv, prm);
+  return (int)cudaGetLastError();
+}
+
+// 0: automatic (the 64-key-tile kernel, the faster one as measured), 1: the same, forced,
+// 2: the persistent 128-key-tile kernel (head_dim 64)
+std::atomic<int> g_prefill_path{0};
+
 template <int D, bool FP16, int MODE>
 int launch_prefill_bwd(const CUtensorMap& x0, const CUtensorMap& x1, const CUtensorMap& y0,
                        const CUtensorMap& y1, const BwdParams& prm, cudaStream_t st) {
@@ -158,7 +192,7 @@ int run_doc_prepass(const void* doc_ids, int doc_is_i64, int64_t sb, int64_t stt
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return SPSATTN_ERR_ALIGN;
   *mono = reinterpret_cast<int*>(workspace);
   *lo = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + prefill_ws_mono_bytes(B));
-  doc_prepass_kernel<<<B, 1024, 0, st>>>(doc_ids, doc_is_i64, sb, stt, N, *lo, *mono);
+  doc_prepass_kernel<<<B, 1024, 0, st>>>(doc_ids, doc_is_i64, sb, stt, N, *lo, *mono, *mono + B);
   return (int)cudaGetLastError();
 }
 
@@ -371,8 +405,10 @@ int spsattn_prefill_fwd_strided(const void* q, const void* k, const void* v, voi
   if (D == 64 || D == 128) {
     CUtensorMap tq, tk, tv;
     if ((rc = encode_q_map(&tq, q, B, H, N, D, sq, dtype)) != 0) return rc;
-    if ((rc = encode_kv_map(&tk, k, B, H, N, D, mask.ks, sk, dtype)) != 0) return rc;
-    if ((rc = encode_kv_map(&tv, v, B, H, N, D, mask.ks, sv, dtype)) != 0) return rc;
+    const bool wide = D == 64 && g_prefill_path.load() == 2;
+    const int box_tokens = wide ? kWideN : kTileN;
+    if ((rc = encode_kv_map(&tk, k, B, H, N, D, mask.ks, sk, dtype, box_tokens)) != 0) return rc;
+    if ((rc = encode_kv_map(&tv, v, B, H, N, D, mask.ks, sv, dtype, box_tokens)) != 0) return rc;
     PrefillParams prm;
     memset(&prm, 0, sizeof(prm));
     prm.o = o;
@@ -396,6 +432,27 @@ int spsattn_prefill_fwd_strided(const void* q, const void* k, const void* v, voi
 #ifdef SPSATTN_TRACE
     prm.trace = g_trace_buffer;
 #endif
+    // heads whose K and V (2 * N * D * 2 bytes each) share about 48 MB of L2 at a time
+    const long long kv_bytes = 4LL * N * D;
+    const long long gh = (48LL << 20) / (kv_bytes > 0 ? kv_bytes : 1);
+    prm.group_heads = (int)(gh < 1 ? 1 : (gh > 32 ? 32 : gh));
+#ifdef SPSATTN_NO_GROUP
+    prm.group_heads = 1;      // tuning builds: one head after the other
+#endif
+    if (wide) {
+      // the item counter lives behind the pre-pass flags: the pre-pass has zeroed it when ids were
+      // given, else it is cleared here; without a workspace the blocks take items with a stride
+      if (mono != nullptr) {
+        prm.work_counter = mono + B;
+      } else if (workspace != nullptr && workspace_bytes >= prefill_ws_mono_bytes(B) &&
+                 (reinterpret_cast<uintptr_t>(workspace) & 3u) == 0) {
+        prm.work_counter = reinterpret_cast<int*>(workspace) + B;
+        cudaError_t me = cudaMemsetAsync(prm.work_counter, 0, sizeof(int), st);
+        if (me != cudaSuccess) return (int)me;
+      }
+      return fp16 ? launch_prefill_wide<true>(tq, tk, tv, prm, st)
+                  : launch_prefill_wide<false>(tq, tk, tv, prm, st);
+    }
     if (D == 64) return fp16 ? launch_prefill_sm100<64, true>(tq, tk, tv, prm, st)
                              : launch_prefill_sm100<64, false>(tq, tk, tv, prm, st);
     return fp16 ? launch_prefill_sm100<128, true>(tq, tk, tv, prm, st)
@@ -770,6 +827,21 @@ int spsattn_decode_step(const void* q, int nq, void* out, int out_dtype, const s
                         void* workspace, size_t workspace_bytes, int* device_status, void* stream) {
   return decode_impl(q, nq, out, out_dtype, segs, n_segments, extras, n_extras, append, true, S, H, D, dtype,
                      sm_scale, workspace, workspace_bytes, device_status, stream);
+}
+
+int spsattn_debug_wait_expiry(int* device_status, unsigned long long limit_ns, int* device_result,
+                              void* stream) {
+  if (device_status == nullptr) return SPSATTN_ERR_ARG;
+  if (limit_ns > 1000000000ull) return SPSATTN_ERR_ARG;    // a test hook: never more than a second
+  wait_expiry_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(device_status, limit_ns,
+                                                                         device_result);
+  return (int)cudaGetLastError();
+}
+
+int spsattn_debug_prefill_path(int path) {
+  if (path < 0 || path > 2) return SPSATTN_ERR_ARG;
+  g_prefill_path.store(path);
+  return 0;
 }
 
 int spsattn_debug_decode_path(int path) {

@@ -36,7 +36,7 @@ import torch
 from torch import Tensor
 
 from . import _lib
-from .attention import _status, prefill_attention
+from .attention import _status, check_device_status, prefill_attention
 
 _VARIANTS = {
     # name: (prediction slot, ring ("window") slot, retained slot, persistent-key parity)
@@ -166,6 +166,9 @@ class DecodeState:
     processed_tokens: Tensor   # [B] int64
     next_doc_start: Tensor     # [B] bool
     max_tokens: int
+    # host-side upper bound of processed_tokens (longest prompt + eager steps taken): lets
+    # decode_one_token refuse a step past the caches or the rotary table without a device sync
+    host_tokens: int = 0
 
 
 class SPSGenerator:
@@ -333,7 +336,11 @@ class SPSGenerator:
         _validate_left_padded(idx, d.pad_token_id, f"{self.variant} generation prefill prompts")
         real = idx != d.pad_token_id
         real_lengths = real.sum(dim=1).to(torch.long)
-        total = int(real_lengths.max().item()) + int(max_new_tokens)
+        longest = int(real_lengths.max().item())
+        # the .item() above has synchronised: a bounded wait that expired in an earlier kernel
+        # shows in the status word now, before its empty outputs are used
+        check_device_status(self.device)
+        total = longest + int(max_new_tokens)
         if total > d.block_size:
             raise ValueError(f"Cannot generate {max_new_tokens} new tokens from a prompt with "
                              f"{total - int(max_new_tokens)} real tokens when block size is {d.block_size}")
@@ -356,6 +363,7 @@ class SPSGenerator:
         next_logits = torch.mm(last, self.w.lm_head.t())
         state.processed_tokens.copy_(real_lengths)
         state.next_doc_start.copy_(idx[:, -1] == d.eos_token_id)
+        state.host_tokens = longest
         return state, next_logits
 
     # ------------------------------------------------------------------ one decode step
@@ -492,7 +500,15 @@ class SPSGenerator:
     @torch.no_grad()
     def decode_one_token(self, state: DecodeState, token_B: Tensor, active_B: Tensor) -> Tensor:
         """Eager form of one step (decode + advance): logits [B, V], zeros for inactive rows as
-        the reference returns them (inference.py:485)."""
+        the reference returns them (inference.py:485).  Raises ValueError, like the reference
+        (inference.py:384-389), when a row could already hold as many tokens as the rotary table
+        or the caches take: past that point the position lookup would read out of range and the
+        cache append would be dropped."""
+        limit = min(self.dims.block_size, state.max_tokens)
+        if state.host_tokens >= limit:
+            raise ValueError(f"Cannot decode another token: up to {state.host_tokens} tokens are processed "
+                             f"and the block size / cache capacity is {limit}")
+        state.host_tokens += 1
         if self._step is None or self._step.state is not state:
             self._bind_step(state)
         s = self._step
@@ -535,6 +551,9 @@ class SPSGenerator:
         key = (b, state.max_tokens, int(max_new_tokens), bool(stop_on_eos), sup, bool(use_graph))
         if g is None or g.state is not state or g.key != key:
             g = self._new_session(state, key)
+        # the captured graph reads and writes the step buffers it was recorded on: the session owns
+        # them, and they are bound again if a decode_one_token on another state replaced them
+        self._step = g.step
         s = self._step
         g.next_logits.copy_(next_logits)
         g.generated.fill_(d.pad_token_id)
@@ -564,8 +583,10 @@ class SPSGenerator:
         ev[3].record()
         self._sample(g)
         ev[4].record()
+        state.host_tokens += n_steps
         if timings is not None:
             torch.cuda.synchronize(self.device)
+            check_device_status(self.device)
             timings["prefill"] = ev[0].elapsed_time(ev[1])
             timings["decode"] = ev[1].elapsed_time(ev[4])        # includes binding and capture, if any
             timings["decode_steps"] = ev[2].elapsed_time(ev[3])  # the n_steps token steps alone
@@ -579,6 +600,7 @@ class SPSGenerator:
             self._bind_step(state)
         g = type("GenerationSession", (), {})()
         g.state, g.key, g.graph = state, key, None
+        g.step = self._step
         g.stop_on_eos = key[3]
         g.suppressed = torch.tensor(list(key[4]), device=dev, dtype=torch.long)
         g.generated = torch.full((b, max_new), d.pad_token_id, device=dev, dtype=torch.long)

@@ -189,10 +189,15 @@ def decode_bytes(lens: np.ndarray, ring: int, heads: int, head_dim: int, nq: int
 
 
 def make_decode(name: str, device, *, seed: int = 0, dtype=torch.bfloat16,
-                seq_slice: Optional[slice] = None) -> DecodeWorkload:
+                seq_slice: Optional[slice] = None, seq_index=None) -> DecodeWorkload:
+    """Build the decode configuration, or this rank's shard of it: `seq_slice` (a contiguous
+    range) or `seq_index` (any list of sequence numbers, e.g. one bin of `balanced_partition`)."""
     S, H, D, ring, lo, hi = DECODE_CONFIGS[name]
     lens = decode_lengths(name, seed)
-    sel = np.arange(S)[seq_slice] if seq_slice is not None else np.arange(S)
+    if seq_index is not None:
+        sel = np.asarray(sorted(int(i) for i in seq_index), dtype=np.int64)
+    else:
+        sel = np.arange(S)[seq_slice] if seq_slice is not None else np.arange(S)
     lens = lens[sel]
     dev = torch.device(device)
     g = torch.Generator(device=dev).manual_seed(seed * 7919 + int(sel[0]) + 1)
@@ -217,3 +222,18 @@ def shard_slice(n_items: int, rank: int, world: int) -> slice:
     base, rem = divmod(n_items, world)
     start = rank * base + min(rank, rem)
     return slice(start, start + base + (1 if rank < rem else 0))
+
+
+def balanced_partition(weights, world: int) -> list:
+    """Split items 0..n-1 into `world` bins of nearly equal total weight: heaviest item first,
+    each into the lightest bin so far (ties: the lower bin).  Returns the sorted item numbers of
+    every bin; used to shard decode sequences by the sum of their cache lengths rather than by
+    their count."""
+    w = np.asarray(weights, dtype=np.float64)
+    bins = [[] for _ in range(world)]
+    load = np.zeros(world)
+    for i in sorted(range(len(w)), key=lambda i: (-w[i], i)):
+        r = int(np.argmin(load))
+        bins[r].append(i)
+        load[r] += w[i]
+    return [sorted(b) for b in bins]

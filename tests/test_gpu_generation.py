@@ -504,3 +504,39 @@ def test_standard_model_greedy_tokens_match_reference(golden, use_graph):
             if float(margins[r, s]) < 0.15:
                 break
             assert int(got[r, 6 + s]) == int(want[r, 6 + s]), (r, s)
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_session_keeps_its_step_buffers_across_a_foreign_decode(golden, use_graph):
+    """generate(), then a prefill and an eager decode_one_token on a second state (which binds other
+    step buffers), then generate() again: the cached session (and its captured graph) must still
+    run on the buffers it was recorded on and give the same tokens."""
+    weights, fields = _golden_model(golden, "sps")
+    eng = _engine(weights, fields, "sps", torch.float32)
+    idx = torch.from_numpy(golden["model_sps_padded_idx"])
+    n_new = 6
+    first = eng.generate(idx, n_new, stop_on_eos=False, use_graph=use_graph).cpu()
+    other, logits = eng.prefill(idx[:1, -4:].contiguous(), 3)
+    tok = logits.float().argmax(dim=-1)
+    eng.decode_one_token(other, tok, torch.ones(1, dtype=torch.bool))
+    again = eng.generate(idx, n_new, stop_on_eos=False, use_graph=use_graph).cpu()
+    assert torch.equal(first, again)
+
+
+def test_decode_one_token_refuses_a_step_past_the_caches(golden):
+    """The reference raises when processed_tokens reaches the block size (reverse_sps/inference.py:
+    384-389); here the bound is kept on the host (longest prompt + steps taken), so the refusal comes
+    before any launch and the out-of-range step never runs on the device."""
+    weights, fields = _golden_model(golden, "sps")
+    eng = _engine(weights, fields, "sps", torch.float32)
+    idx = torch.from_numpy(golden["model_sps_padded_idx"])[:1, -4:].contiguous()
+    state, logits = eng.prefill(idx, 2)            # caches hold the prompt + 2 tokens
+    tok = logits.float().argmax(dim=-1)
+    on = torch.ones(1, dtype=torch.bool)
+    longest = int((idx != fields["pad_token_id"]).sum())
+    assert state.host_tokens == longest and state.max_tokens == longest + 2
+    eng.decode_one_token(state, tok, on)
+    eng.decode_one_token(state, tok, on)
+    with pytest.raises(ValueError, match="Cannot decode another token"):
+        eng.decode_one_token(state, tok, on)
+    torch.cuda.synchronize()

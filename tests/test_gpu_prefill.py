@@ -34,6 +34,17 @@ def _cuda(a, dtype):
     return torch.from_numpy(np.ascontiguousarray(a)).to(_dev()).to(dtype)
 
 
+@pytest.fixture(params=[0, 2], ids=["tiles64", "persistent128"], autouse=True)
+def prefill_kernel(request):
+    """Every test of this file runs against both tensor-core kernels that serve head_dim 64: the
+    default one (64-key tiles) and the persistent one (128-key tiles, P in tensor memory)."""
+    from sps_b200 import _lib
+    lib = _lib.load()
+    _lib.check(lib.spsattn_debug_prefill_path(request.param), "spsattn_debug_prefill_path")
+    yield request.param
+    _lib.check(lib.spsattn_debug_prefill_path(0), "spsattn_debug_prefill_path")
+
+
 @pytest.mark.parametrize("tag", ["nodoc", "doc", "n8", "n24", "n200", "n384"])
 def test_sps_matches_reference_vectors(golden, tag):
     import sps_b200
