@@ -39,8 +39,9 @@ GENERATION = "cfg3_xl_generation"
 # processed (traffic is proportional to batch rows / sequences)
 PREFILL_DRAM_BYTES_PER_LAUNCH = 2 * (151.4e6 + 33.3e6)
 DECODE_DRAM_BYTES_PER_LAUNCH = 4 * (332.2e6 + 4.9e6)
+# head_dim 128 forward: ncu dram bytes of a 4-head launch (quarter of the heads) x4
+FULL_WINDOW_DRAM_BYTES_PER_LAUNCH = 4 * (100.7e6 + 15.4e6)
 # dK/dV kernel + dQ kernel of one backward call: ncu dram bytes of a 4-row call x2
-# (profiles/prefill_bwd_sm100_d64_cfg1_half_batch.md)
 BACKWARD_DRAM_BYTES_PER_CALL = 2 * (204.8e6 + 76.8e6 + 204.7e6 + 36.4e6)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -68,7 +69,7 @@ while True:
     try:
         c = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
         r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-        sys.stdout.write("%.6f %d %d\\n" % (time.time(), c, r))
+        sys.stdout.write("%.6f %d %d\n" % (time.time(), c, r))
         sys.stdout.flush()
     except Exception:
         pass
@@ -209,6 +210,112 @@ def timed_steps(fn, steps, warmup, world, device, regions=5, sampler=None):
 
 # ------------------------------------------------------------------------------------- ours
 
+def headline_config(world: int) -> dict:
+    """The `config` object of the JSON line; both arms print exactly this for the same --gpus."""
+    from sps_b200 import workloads
+    B, H, T, D, w, _ = workloads.PREFILL_CONFIGS[PREFILL]
+    docs = workloads.geometric_docs(B, T, 1000, 0)
+    flops = workloads.prefill_flops(workloads.useful_pairs(docs, w), H, D)
+    return {
+        "workload": f"{PREFILL}: SPS prefill attention [B={B},H={H},2T={2 * T},D={D}] bf16, w={w}, "
+                    "documents ~ Geometric(mean 1000 tokens), reference mask rule, per GPU",
+        "useful_gflop_per_step_per_gpu": flops / 1e9,
+        "l2": f"inputs larger than L2: {4 * B * H * 2 * T * D * 2 / 1e6:.0f} MB of Q/K/V/O per step vs 126 MB",
+        "parallelism": f"independent shards x{world}, no collective",
+    }
+
+
+def _prefill_fn(sps_b200, wl, out, docs=True):
+    return lambda: sps_b200.prefill_attention(wl.q, wl.k, wl.v, wl.sm_scale, persistent_parity=0,
+                                              temporary_window=wl.window,
+                                              documents_idx=wl.docs if docs else None, out=out)
+
+
+def strong_prefill(sps_b200, workloads, name, axis, world, rank, device, steps):
+    """The north-star split of one prefill configuration: the fixed total problem cut over the
+    ranks by batch rows or by heads (shards are independent, no collective); aggregate rate =
+    useful FLOPs of the whole problem / slowest rank's time."""
+    B, H = workloads.PREFILL_CONFIGS[name][:2]
+    n = B if axis == "batch" else H
+    sl = workloads.shard_slice(n, rank, world)
+    if sl.stop <= sl.start:
+        raise RuntimeError(f"{name}: more ranks than {axis} items")
+    kw = {"batch_slice": sl} if axis == "batch" else {"head_slice": sl}
+    wl = workloads.make_prefill(name, device, **kw)
+    out = torch.empty_like(wl.q)
+    region_ms, launch_ms, det = timed_steps(_prefill_fn(sps_b200, wl, out, wl.docs is not None), steps, 3,
+                                            world, device, regions=3)
+    total = _sum_over_ranks(wl.flops, world, device)
+    return {"split": f"{axis} {n} -> {sl.stop - sl.start} per GPU", "useful_tflops": total * steps / (region_ms * 1e-3) / 1e12,
+            "ms_per_step": region_ms / steps, "launch_ms_this_rank": launch_ms, "timing": det,
+            "note": "strong scaling: the per-GPU launch shrinks with N (at 1 batch row x 12 heads a launch is "
+                    "768 blocks = 1.7 waves), so launch latency and the tail show here"}
+
+
+def reference_triton(device):
+    """The reference's own Triton kernels on this GPU, same inputs, CUDA events, after their
+    autotune warm-up: the existing Blackwell path the kernels of this repository replace.  Needs
+    the reference installed under baseline/_ref and an importable triton; otherwise the reason."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "modeling", "models")):
+        return {"unavailable": "unavailable on this box: baseline/_ref holds no install of the reference"}
+    try:
+        import triton                                                                  # noqa: F401
+        if ref_dir not in sys.path:
+            sys.path.insert(0, ref_dir)
+        from modeling.models.attention.triton_sps_flash_attention import sps_sliding_attention as ref_sps
+        from modeling.models.utils.decode_attention import KVSegment as RefSegment
+        from modeling.models.utils.decode_attention import triton_segmented_q2_attention as ref_q2
+    except Exception as e:
+        return {"unavailable": f"unavailable on this box: {e!r}"}
+    import sps_b200
+    from sps_b200 import workloads
+    out = {"triton": triton.__version__, "how": "3 warm-up calls (autotune), 10 timed calls, CUDA events; "
+                                                 "warp_specialize=False as the reference's configs run it"}
+
+    def time_it(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            r = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 10, r
+
+    for name in (PREFILL, PREFILL_FULL_WINDOW):
+        try:
+            wl = workloads.make_prefill(name, device)
+            ms, o_ref = time_it(lambda: ref_sps(wl.q, wl.k, wl.v, wl.sm_scale, wl.window, False, wl.docs, None))
+            o_our = sps_b200.sps_sliding_attention(wl.q, wl.k, wl.v, wl.sm_scale, wl.window, False, wl.docs, None)
+            diff = (o_ref.float() - o_our.float()).abs()
+            out[name] = {"ms": ms, "useful_tflops": wl.flops / (ms * 1e-3) / 1e12,
+                         "max_abs_diff_vs_this_repo": float(diff.max()), "mean_abs_diff_vs_this_repo": float(diff.mean())}
+            del wl, o_ref, o_our, diff
+        except Exception as e:
+            out[name] = {"unavailable": f"unavailable on this box: {e!r}"}
+        torch.cuda.empty_cache()
+    try:
+        dw = workloads.make_decode(DECODE, device)
+        mk = lambda cls: [cls(dw.ring_k, dw.ring_v, dw.ring_len, max_len_cap=dw.ring_k.shape[2]),
+                          cls(dw.cache_k, dw.cache_v, dw.cache_len, max_len_cap=dw.cache_k.shape[2])]
+        kw = dict(current_normal_k_BxHxD=dw.cur_k, current_normal_v_BxHxD=dw.cur_v,
+                  current_predict_k_BxHxD=dw.pred_k, current_predict_v_BxHxD=dw.pred_v, attn_dtype=torch.bfloat16)
+        rsegs = mk(RefSegment)
+        ms, o_ref = time_it(lambda: ref_q2(dw.q, rsegs, **kw))
+        o_our = sps_b200.segmented_q2_attention(dw.q, mk(sps_b200.KVSegment), **kw)
+        out[DECODE] = {"ms": ms, "gb_per_s": dw.bytes / (ms * 1e-3) / 1e9,
+                       "tokens_per_s": dw.q.shape[0] / (ms * 1e-3),
+                       "max_abs_diff_vs_this_repo": float((o_ref - o_our).abs().max())}
+        del dw, rsegs, o_ref, o_our
+    except Exception as e:
+        out[DECODE] = {"unavailable": f"unavailable on this box: {e!r}"}
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
     import sps_b200
     from sps_b200 import workloads
@@ -218,44 +325,41 @@ def run_ours(args):
     device = torch.device("cuda", local)
     peaks, peak_kind = load_peaks()
     K, W = args.steps, max(args.warmup, 3)
-
-    # ---------------- prefill (headline)
+    # ---------------- prefill (headline): every rank the full configuration on its own shard
+    sampler = ClockSampler(local)
     wl = workloads.make_prefill(PREFILL, device, seed=rank)
     out = torch.empty_like(wl.q)
-
-    def prefill_step():
-        sps_b200.prefill_attention(wl.q, wl.k, wl.v, wl.sm_scale, persistent_parity=0,
-                                   temporary_window=wl.window, documents_idx=wl.docs, out=out)
-
-    with ClockSampler(local) as clk:
-        region_ms, launch_ms = timed_steps(prefill_step, K, W, world, device)
+    region_ms, launch_ms, det = timed_steps(_prefill_fn(sps_b200, wl, out), K, W, world, device,
+                                            regions=5, sampler=sampler)
+    clocks = sampler.summary()
     sps_b200.check_device_status(device)
     flops_all = wl.flops if world == 1 else _sum_over_ranks(wl.flops, world, device)
     value = flops_all * K / (region_ms * 1e-3) / 1e12
     achieved = wl.flops / (launch_ms * 1e-3) / 1e12
     peak = float(peaks["bf16_tflops"])
-    B, H, N, D = wl.q.shape
     result = {
         "metric": "sps_prefill_useful_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": K, "warmup": W, "ms_per_step": region_ms / K, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {
-            "workload": f"{PREFILL}: SPS prefill attention [B={B},H={H},2T={N},D={D}] bf16, w={wl.window}, "
-                        "documents ~ Geometric(mean 1000 tokens), reference mask rule, per GPU",
-            "useful_gflop_per_step_per_gpu": wl.flops / 1e9,
-            "l2": f"inputs larger than L2: {4 * wl.q.numel() * 2 / 1e6:.0f} MB of Q/K/V/O per step vs 126 MB",
-            "parallelism": f"independent shards x{world}, no collective",
-        },
-        "clocks": clk.summary(),
+        "config": headline_config(world),
+        "clocks": clocks,
         "gpu_launches": 2 * K,      # document pre-pass + attention kernel per step
+        "timing": dict(det, note="5 back-to-back regions of K steps, each bracketed by barrier + synchronize; "
+                                 "the median region (by its max over ranks) is the one reported"),
         "roofline": {
             "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": achieved / peak, "traffic": PREFILL_DRAM_BYTES_PER_LAUNCH,
-            "traffic_source": "ncu dram__bytes_read+write of a 4-row launch x2 (profiles/prefill_sm100_d64_cfg1_half_batch.md)",
+            "traffic_source": "ncu dram__bytes_read+write of a 4-row launch (half-batch case) x2",
             "peak_source": f"{peak_kind} bf16 burst (kernel timed alone)",
             "launch_ms": launch_ms,
         },
     }
+    if world > 1:
+        del wl, out
+        torch.cuda.empty_cache()
+        result["strong"] = strong_prefill(sps_b200, workloads, PREFILL, "batch", world, rank, device, max(3, min(K, 30)))
+        wl = workloads.make_prefill(PREFILL, device, seed=rank)
+        out = torch.empty_like(wl.q)
 
     # ---------------- end to end through the public API with host buffers
     # Every step copies its Q, K, V and document ids from pinned host memory, calls the public
@@ -333,7 +437,7 @@ def run_ours(args):
                 temporary_window=wl.window, documents_idx=wl.docs)
 
         kb = max(3, min(K, 30))
-        b_region, b_launch = timed_steps(backward_step, kb, 3, world, device)
+        b_region, b_launch, _ = timed_steps(backward_step, kb, 3, world, device, regions=3)
         # five products per visible (query, key) pair against the forward's two
         b_flops = 2.5 * wl.flops
         tb = b_flops / (b_launch * 1e-3) / 1e12
@@ -345,8 +449,8 @@ def run_ours(args):
             "gpu_launches": 5 * kb,      # document pre-pass, run ends, delta, dK/dV, dQ
             "roofline": {"bound": "tensor", "achieved": tb, "peak": peak, "unit": "TFLOP/s", "frac": tb / peak,
                          "traffic": BACKWARD_DRAM_BYTES_PER_CALL,
-                         "traffic_source": "ncu dram__bytes_read+write of the two kernels of a 4-row call x2 "
-                                           "(profiles/prefill_bwd_sm100_d64_cfg1_half_batch.md)",
+                         "traffic_source": "ncu dram__bytes_read+write of the two kernels of a 4-row call "
+                                           "(half-batch case) x2",
                          "peak_source": f"{peak_kind} bf16 burst", "launch_ms": b_launch,
                          "note": "useful FLOPs = 2.5 x forward; the two kernels recompute S and dP, so they "
                                  "execute 3.5 x forward"},
@@ -360,39 +464,40 @@ def run_ours(args):
         torch.cuda.empty_cache()
         wf = workloads.make_prefill(PREFILL_FULL_WINDOW, device, seed=rank)
         outf = torch.empty_like(wf.q)
-
-        def full_window_step():
-            sps_b200.prefill_attention(wf.q, wf.k, wf.v, wf.sm_scale, persistent_parity=0,
-                                       temporary_window=wf.window, documents_idx=None, out=outf)
-
         kf = max(3, min(K, 30))
-        f_region, f_launch = timed_steps(full_window_step, kf, 3, world, device)
+        f_region, f_launch, _ = timed_steps(_prefill_fn(sps_b200, wf, outf, False), kf, 3, world, device, regions=3)
         tf = wf.flops / (f_launch * 1e-3) / 1e12
         result["prefill_full_window"] = {
             "workload": f"{PREFILL_FULL_WINDOW}: [B=4,H=16,2T=8192,D=128] bf16, w=4096, one document per row, per GPU",
             "useful_gflop_per_step_per_gpu": wf.flops / 1e9, "ms_per_step": f_region / kf,
             "useful_tflops": world * wf.flops * kf / (f_region * 1e-3) / 1e12, "gpu_launches": kf,
             "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
-                         "traffic": None, "peak_source": f"{peak_kind} bf16 burst", "launch_ms": f_launch},
+                         "traffic": FULL_WINDOW_DRAM_BYTES_PER_LAUNCH,
+                         "traffic_source": "ncu dram__bytes_read+write of a 4-head launch (quarter-heads case) x4",
+                         "peak_source": f"{peak_kind} bf16 burst", "launch_ms": f_launch},
         }
         wl = out = None
         del wf, outf
+        torch.cuda.empty_cache()
+        if world > 1:
+            result["prefill_full_window"]["strong"] = strong_prefill(
+                sps_b200, workloads, PREFILL_FULL_WINDOW, "heads", world, rank, device, kf)
 
     # ---------------- segmented decode step (second half of the metric)
     if not args.skip_decode:
         wl = out = None
         torch.cuda.empty_cache()
-        dw = workloads.make_decode(DECODE, device, seed=rank)
-        segs = [sps_b200.KVSegment(dw.ring_k, dw.ring_v, dw.ring_len, max_len_cap=dw.ring_k.shape[2]),
-                sps_b200.KVSegment(dw.cache_k, dw.cache_v, dw.cache_len, max_len_cap=dw.cache_k.shape[2])]
 
-        def decode_step():
-            sps_b200.segmented_q2_attention(
+        def decode_leg(dw, steps, warm, regions):
+            segs = [sps_b200.KVSegment(dw.ring_k, dw.ring_v, dw.ring_len, max_len_cap=dw.ring_k.shape[2]),
+                    sps_b200.KVSegment(dw.cache_k, dw.cache_v, dw.cache_len, max_len_cap=dw.cache_k.shape[2])]
+            fn = lambda: sps_b200.segmented_q2_attention(
                 dw.q, segs, current_normal_k_BxHxD=dw.cur_k, current_normal_v_BxHxD=dw.cur_v,
-                current_predict_k_BxHxD=dw.pred_k, current_predict_v_BxHxD=dw.pred_v,
-                attn_dtype=torch.bfloat16)
+                current_predict_k_BxHxD=dw.pred_k, current_predict_v_BxHxD=dw.pred_v, attn_dtype=torch.bfloat16)
+            return timed_steps(fn, steps, warm, world, device, regions=regions)
 
-        d_region, d_launch = timed_steps(decode_step, K, W, world, device)
+        dw = workloads.make_decode(DECODE, device, seed=rank)
+        d_region, d_launch, _ = decode_leg(dw, K, W, 3)
         S = dw.q.shape[0]
         gbs = dw.bytes / (d_launch * 1e-3) / 1e9
         hbm = float(peaks["hbm_gbs"])
@@ -403,17 +508,38 @@ def run_ours(args):
             "algorithmic_mb_per_step": dw.bytes / 1e6, "gpu_launches": K,   # one launch per step
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
                          "traffic": DECODE_DRAM_BYTES_PER_LAUNCH,
-                         "traffic_source": "ncu dram__bytes_read+write of a 32-sequence launch x4 "
-                                           "(profiles/decode_tc_d64_cfg2_32seq.md)",
+                         "traffic_source": "ncu dram__bytes_read+write of a 32-sequence launch x4",
                          "peak_source": f"{peak_kind} copy bandwidth", "launch_ms": d_launch},
         }
         sps_b200.check_device_status(device)
+        if world > 1:
+            del dw
+            torch.cuda.empty_cache()
+            bins = workloads.balanced_partition(workloads.decode_lengths(DECODE), world)
+            ds = workloads.make_decode(DECODE, device, seq_index=bins[rank])
+            s_region, s_launch, s_det = decode_leg(ds, K, 3, 3)
+            result["decode"]["strong"] = {
+                "split": f"128 sequences in {world} bins of equal summed cache length (heaviest first into the "
+                         f"lightest bin): {len(bins[rank])} sequences on this rank",
+                "tokens_per_s": 128 * K / (s_region * 1e-3), "ms_per_step": s_region / K,
+                "launch_ms_this_rank": s_launch, "timing": s_det}
+            del ds
+        elif not args.skip_cpu_baseline:
+            result["decode"]["cpu_baseline"] = cpu_baseline_decode(dw, budget_s=8.0)
+            del dw
 
     # ---------------- whole-model greedy generation with the attention path inside
     if not args.skip_generation:
-        wl = out = dw = segs = None
+        wl = out = dw = None
         torch.cuda.empty_cache()
         result["generation"] = run_generation(GENERATION, world, rank, device, peaks, peak_kind)
+        if world == 1 and not args.skip_cpu_baseline:
+            result["generation"]["cpu_baseline"] = cpu_baseline_generation(budget_s=10.0)
+
+    # ---------------- the reference's own Triton kernels on the same GPU (rank 0, one GPU)
+    if world == 1 and not args.skip_reference_triton:
+        torch.cuda.empty_cache()
+        result["reference_triton"] = reference_triton(device)
 
     # ---------------- CPU baseline beside it (rank 0, single GPU runs only)
     if world == 1 and not args.skip_cpu_baseline:
@@ -550,7 +676,7 @@ def run_case(args):
             dw.q, segs, current_normal_k_BxHxD=dw.cur_k, current_normal_v_BxHxD=dw.cur_v,
             current_predict_k_BxHxD=dw.pred_k, current_predict_v_BxHxD=dw.pred_v, attn_dtype=torch.bfloat16)
         work, unit = dw.bytes / 1e9, "GB/s"
-    _, launch_ms = timed_steps(fn, args.steps, max(args.warmup, 1), 1, device)
+    _, launch_ms, _ = timed_steps(fn, args.steps, max(args.warmup, 1), 1, device, regions=1)
     sps_b200.check_device_status(device)
     print(json.dumps({"case": args.case, "launch_ms": launch_ms, "work": work,
                       "achieved": work / (launch_ms * 1e-3), "unit": unit}))
@@ -565,27 +691,52 @@ def _sum_over_ranks(x, world, device):
 
 # -------------------------------------------------------------------------- CPU baseline
 
-def cpu_sample(n_heads: int):
-    """One bounded sample of the prefill workload on the host: batch row 0, the first `n_heads`
-    heads, full length (2T = 8192), through the dense-mask + SDPA formulation."""
-    from oracle import sps_oracle as orc
+def _reference_cpu_modules():
+    """The reference's own CPU formulations, when its package is installed under baseline/_ref:
+    (its SDPA test oracle for SPS attention, its masked_kv_attention + KVSegment), else None."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "modeling", "models")):
+        return None
+    try:
+        if ref_dir not in sys.path:
+            sys.path.insert(0, ref_dir)
+        from modeling.models.utils.decode_attention import KVSegment, masked_kv_attention
+        from modeling.tests.attention.triton.test_sps_attention import _sdpa_reference_attention_sps
+        return _sdpa_reference_attention_sps, masked_kv_attention, KVSegment
+    except Exception:
+        return None
+
+
+CPU_SAMPLE_HEADS = 2
+
+
+def cpu_sample():
+    """One bounded sample of the prefill workload on the host: batch row 0, the first two heads,
+    full length (2T = 8192), through the dense additive mask + SDPA formulation: the reference's
+    own function (src/modeling/tests/attention/triton/test_sps_attention.py:25-74) when its
+    package is installed under baseline/_ref, else the restatement in oracle/.  Returns
+    (callable, useful FLOPs of one call, kind, description)."""
     from sps_b200 import workloads
     B, H, T, D, w, mean = workloads.PREFILL_CONFIGS[PREFILL]
+    n_heads = CPU_SAMPLE_HEADS
     docs = workloads.geometric_docs(B, T, mean, 0)[:1]
     g = torch.Generator().manual_seed(0)
     q, k, v = (torch.randn(1, n_heads, 2 * T, D, generator=g) for _ in range(3))
     flops = workloads.prefill_flops(workloads.useful_pairs(docs, w), n_heads, D)
     dd = torch.from_numpy(docs)
-
-    def run():
-        return orc.prefill_attention_sdpa(q, k, v, 1.0 / np.sqrt(D), temporary_window=w, docs=dd)
-
-    return run, flops
+    what = f"{PREFILL} batch row 0, heads 0-{n_heads - 1}, full length {2 * T} per step: dense additive mask + torch SDPA fp32"
+    ref = _reference_cpu_modules()
+    if ref is not None:
+        fn = ref[0]
+        return (lambda: fn(q, k, v, w, dd)), flops, "reference", what + " (the reference's _sdpa_reference_attention_sps)"
+    from oracle import sps_oracle as orc
+    return (lambda: orc.prefill_attention_sdpa(q, k, v, 1.0 / np.sqrt(D), temporary_window=w, docs=dd)), flops, \
+        "port", what + " (the reference's CPU formulation restated in oracle/)"
 
 
 def cpu_baseline(budget_s: float):
     torch.set_num_threads(os.cpu_count() or 1)
-    run, flops = cpu_sample(2)
+    run, flops, kind, what = cpu_sample()
     run()                                   # warm-up
     t0, n = time.perf_counter(), 0
     while True:
@@ -594,41 +745,106 @@ def cpu_baseline(budget_s: float):
         if time.perf_counter() - t0 > budget_s or n >= 50:
             break
     dt = (time.perf_counter() - t0) / n
-    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{PREFILL} batch row 0, heads 0-1, full length 8192: dense additive mask + "
-                      f"torch SDPA fp32 (the reference's CPU formulation), {n} passes of {dt:.2f} s",
-            "seconds_per_pass": dt}
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
+            "sample": f"{what}, {n} passes of {dt:.2f} s", "seconds_per_pass": dt}
+
+
+def cpu_baseline_decode(dw, budget_s: float, n_seq: int = 8):
+    """The decode step on the host for the first `n_seq` sequences of the workload: the
+    reference's SDPA fallback (masked_kv_attention, src/modeling/models/utils/decode_attention.py:
+    637-704), once per query as the reference's callers use it, or its restatement in oracle/.
+    GB/s on the same algorithmic bytes as the GPU figure."""
+    from sps_b200 import workloads
+    torch.set_num_threads(os.cpu_count() or 1)
+    sl = slice(0, n_seq)
+    t = {n: getattr(dw, n)[sl].cpu() for n in ("q", "cache_k", "cache_v", "cache_len", "ring_k", "ring_v", "ring_len",
+                                                "cur_k", "cur_v", "pred_k", "pred_v")}
+    H, D, ring = t["q"].shape[2], t["q"].shape[3], t["ring_k"].shape[2]
+    nbytes = workloads.decode_bytes(dw.lens_np[sl], ring, H, D)
+    ref = _reference_cpu_modules()
+    if ref is not None:
+        _, mkv, Seg = ref
+        f32 = {n: (x.float() if x.is_floating_point() else x) for n, x in t.items()}
+        segs = [Seg(f32["ring_k"], f32["ring_v"], f32["ring_len"], max_len_cap=ring),
+                Seg(f32["cache_k"], f32["cache_v"], f32["cache_len"], max_len_cap=f32["cache_k"].shape[2])]
+
+        def run():
+            mkv(f32["q"][:, 0], segs, extra_kv=[(f32["cur_k"], f32["cur_v"])], attn_dtype=torch.float32)
+            mkv(f32["q"][:, 1], segs, extra_kv=[(f32["cur_k"], f32["cur_v"]), (f32["pred_k"], f32["pred_v"])],
+                attn_dtype=torch.float32)
+        kind, what = "reference", "the reference's masked_kv_attention SDPA fallback, one call per query"
+    else:
+        from oracle import sps_oracle as orc
+
+        def run():
+            orc.decode_attention_batched(t["q"], t["cache_k"], t["cache_v"], t["cache_len"], t["ring_k"], t["ring_v"],
+                                         t["ring_len"], t["cur_k"], t["cur_v"], t["pred_k"], t["pred_v"])
+        kind, what = "port", "padded K/V + boolean mask + torch SDPA fp32 (the reference's fallback restated in oracle/)"
+    run()
+    t0, n = time.perf_counter(), 0
+    while True:
+        run()
+        n += 1
+        if time.perf_counter() - t0 > budget_s or n >= 50:
+            break
+    dt = (time.perf_counter() - t0) / n
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "tokens_per_s": n_seq / dt, "cores": torch.get_num_threads(),
+            "kind": kind, "sample": f"{DECODE} sequences 0-{n_seq - 1} of 128 (padded to 4096 rows): {what}, "
+                                    f"{n} passes of {dt:.2f} s"}
+
+
+def cpu_baseline_generation(budget_s: float):
+    """Greedy generation of the model-level CPU oracle (oracle/sps_model_oracle.py: dense re-forward
+    per token in fp32, the attention oracle inside) on a labelled reduced size: tokens/s."""
+    from oracle import sps_model_oracle as mo
+    from sps_b200 import workloads
+    from sps_b200.generation import SPSDims, random_state_dict
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = workloads.GENERATION_CONFIGS["generation_small"]
+    fields = {k: cfg[k] for k in ("block_size", "vocab_size", "n_layer", "n_head", "hidden_size", "intermediate_size",
+                                  "eos_token_id", "pad_token_id", "predict_token_id", "window_size")}
+    sd = {k: v.float() for k, v in random_state_dict(SPSDims(**fields), seed=0, device="cpu").items()}
+    dims = mo.Dims(**fields)
+    batch, new = 2, 4
+    prompts = torch.from_numpy(workloads.generation_prompts(cfg, batch, 0))
+    t0, n = time.perf_counter(), 0
+    while True:
+        mo.generate(sd, dims, prompts, new, variant="sps", stop_on_eos=False)
+        n += 1
+        if time.perf_counter() - t0 > budget_s or n >= 20:
+            break
+    dt = (time.perf_counter() - t0) / n
+    return {"value": batch * new / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"REDUCED SIZE (generation_small: {fields['n_layer']} layers, hidden {fields['hidden_size']}, "
+                      f"{fields['n_head']} heads, prompt {cfg['prompt']}, batch {batch}, {new} new tokens): the model "
+                      f"oracle's greedy generation (dense fp32 re-forward per token), {n} passes of {dt:.2f} s; the "
+                      "reference's model classes have no CPU path for the fused decode step"}
 
 
 def run_reference(args):
-    """The reference's CPU path for this workload on the host cores: rank 0 only."""
+    """The reference's CPU path for this workload on the host cores: rank 0 only.  Same metric,
+    unit and config object as the other arm; every step is the bounded sample of `cpu_sample`."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
-    from sps_b200 import workloads
-    K, W = args.steps, args.warmup
-    run, flops = cpu_sample(1)
-    for _ in range(min(W, 2)):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    K, W = max(1, args.steps), max(args.warmup, 3)
+    run, flops, kind, what = cpu_sample()
+    for _ in range(W):
         run()
-    K = max(1, min(K, 20))
     t0 = time.perf_counter()
     for _ in range(K):
         run()
     dt = time.perf_counter() - t0
     value = flops * K / dt / 1e12
-    B, H, T, D, w, _ = workloads.PREFILL_CONFIGS[PREFILL]
-    sample = f"{PREFILL} batch row 0, head 0, full length {2 * T} per step"
     print(json.dumps({
         "impl": "reference", "metric": "sps_prefill_useful_tflops", "value": value, "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": K, "warmup": min(W, 2), "ms_per_step": dt / K * 1e3,
+        "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": dt / K * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{PREFILL}: SPS prefill attention [B={B},H={H},2T={2 * T},D={D}] bf16, w={w}, "
-                               "documents ~ Geometric(mean 1000 tokens), reference mask rule, per GPU",
-                   "cpu_sample": sample},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample + ": dense additive mask + torch SDPA fp32 "
-                                            "(the reference's CPU formulation restated in oracle/)"},
+        "config": headline_config(world),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
+                         "sample": what},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -646,6 +862,10 @@ def main():
     ap.add_argument("--skip-full-window", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-generation", action="store_true")
+    ap.add_argument("--skip-reference-triton", action="store_true",
+                    help="do not time the reference's Triton kernels (baseline/_ref) beside ours")
+    ap.add_argument("--prefill-path", choices=["auto", "tiles64", "persistent128"], default="auto",
+                    help="tensor-core prefill kernel at head_dim 64 (auto: the 64-key-tile kernel)")
     ap.add_argument("--decode-path", choices=["auto", "cuda-core", "tensor-core"], default="auto",
                     help="decode kernel behind the decode step (auto: tensor cores at head_dim 64)")
     ap.add_argument("--new-tokens", type=int, default=None, help="generation cases: tokens to generate")
@@ -655,6 +875,10 @@ def main():
         from sps_b200 import _lib
         _lib.check(_lib.load().spsattn_debug_decode_path({"cuda-core": 1, "tensor-core": 2}[args.decode_path]),
                    "spsattn_debug_decode_path")
+    if args.prefill_path != "auto" and args.impl == "ours":
+        from sps_b200 import _lib
+        _lib.check(_lib.load().spsattn_debug_prefill_path({"tiles64": 1, "persistent128": 2}[args.prefill_path]),
+                   "spsattn_debug_prefill_path")
     if args.impl == "reference":
         run_reference(args)
     elif args.case != "full":

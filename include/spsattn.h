@@ -212,8 +212,10 @@ int spsattn_decode_fwd(const void* q, int nq, float* out,
  * sequences over several calls or use spsattn_decode_fwd.  Every GPU that loads the library
  * carries the 16 MiB until the process exits.
  *
- * The first call on each device looks up the buffer's device address (the device must be
- * current, as for every call); make that first call outside any stream capture.  All calls on a
+ * Every call looks up the buffer's device address on the current device (the device must be
+ * current, as for every call), so the address is never stale after a device reset; the first
+ * call on a device also sets the library's code up there: make that first call outside any
+ * stream capture.  All calls on a
  * device share the one buffer: calls that can overlap on the GPU (different streams, no ordering
  * between them) race on it and must be serialised by the caller.  The buffer keeps the previous
  * call's records; nothing in it has to start at zero, because a call only reads records it has

@@ -974,25 +974,15 @@ int spsattn_fill_decode_caches(const void* k, const void* v, int64_t stride_b, i
 static __device__ __align__(256) unsigned char g_noalloc_scratch[SPSATTN_NOALLOC_SCRATCH_BYTES];
 
 namespace {
-constexpr int kNoAllocMaxDevices = 64;
-std::mutex g_noalloc_mutex;
-void* g_noalloc_ptr[kNoAllocMaxDevices] = {};
-
-// Device address of the scratch buffer on the current device; looked up once per device.
+// Device address of the scratch buffer on the current device.  Looked up on every call: after the
+// first call on a device (which loads the module there) this is a host-side table look-up, and
+// an address cached across cudaDeviceReset or a new context would be stale.
 int noalloc_scratch_ptr(void** out) {
-  int dev = -1;
-  cudaError_t e = cudaGetDevice(&dev);
+  void* ptr = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
   if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= kNoAllocMaxDevices) return SPSATTN_ERR_TOO_LARGE;
-  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
-  if (g_noalloc_ptr[dev] == nullptr) {
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
-    if (e != cudaSuccess) return (int)e;
-    if (ptr == nullptr) return SPSATTN_ERR_ARG;
-    g_noalloc_ptr[dev] = ptr;
-  }
-  *out = g_noalloc_ptr[dev];
+  if (ptr == nullptr) return SPSATTN_ERR_ARG;
+  *out = ptr;
   return 0;
 }
 }  // namespace

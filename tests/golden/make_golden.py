@@ -2,7 +2,7 @@
 writes just the second) from the reference's own CPU oracles.
 
 Run once, in a container that has the reference checkout (it cannot travel to
-the GPU box, so the vectors are committed):
+another machine, so the vectors are committed):
 
     REFERENCE_ROOT=/path/to/reference python tests/golden/make_golden.py
 

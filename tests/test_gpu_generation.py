@@ -366,6 +366,42 @@ def test_engine_matches_model_oracle_on_a_larger_case(variant, hd):
     assert torch.equal(state.nw_len.cpu(), live.clamp(max=8).view(1, 3).expand(2, 3))
 
 
+def test_engine_at_the_width_of_the_generation_benchmark():
+    """The generation benchmark's layer width (hidden 2048, 16 heads x 128, SwiGLU 8192, window 64,
+    the reference's N(0, 0.02) initialisation) on two layers, a prompt of 256 tokens with left
+    padding in one row and an EOS inside the other: prefill logits and the logits of 8
+    teacher-forced decode steps (tokens chosen greedily by the oracle) against the pinned CPU
+    oracle of the model.  The 24-layer model of the benchmark is this block repeated."""
+    from sps_b200.generation import SPSDims, random_state_dict
+    fields = dict(block_size=320, vocab_size=4096, n_layer=2, n_head=16, hidden_size=2048,
+                  intermediate_size=8192, eos_token_id=4000, pad_token_id=4095, predict_token_id=4001,
+                  window_size=64)
+    sd = {k: v.float() for k, v in random_state_dict(SPSDims(**fields), seed=3, device="cpu",
+                                                     dtype=torch.float32).items()}
+    dims = mo.Dims(**fields)
+    g = torch.Generator().manual_seed(12)
+    idx = torch.randint(0, 4000, (2, 256), generator=g)
+    idx[0, :19] = fields["pad_token_id"]
+    idx[1, 101] = fields["eos_token_id"]
+    eng = _engine(sd, fields, "sps", torch.float32)
+    n_new = 9
+    state, logits = eng.prefill(idx, max_new_tokens=n_new)
+    seq = idx.clone()
+    on = torch.ones(2, dtype=torch.bool)
+    for step in range(n_new):
+        pos = mo.left_padded_positions(seq, dims.pad_token_id)
+        ref = mo.logits(sd, dims, seq, variant="sps", positions=pos)[:, -1]
+        err = (logits.float().cpu() - ref).abs()
+        assert float(err.max()) <= 3e-2 + 2e-2 * float(ref.abs().max()), (step, float(err.max()))
+        assert float(err.mean()) <= 4e-3, (step, float(err.mean()))
+        tok = mo.greedy_token(ref, dims)
+        seq = torch.cat([seq, tok[:, None]], dim=1)
+        if step + 1 < n_new:
+            logits = eng.decode_one_token(state, tok, on)
+    import sps_b200
+    sps_b200.check_device_status()
+
+
 def test_bf16_parameters_track_the_fp32_run(golden):
     """bf16 parameters (how the reference generates on CUDA): logits stay within bf16 noise of the
     fp32-parameter run and of the reference."""

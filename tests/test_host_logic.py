@@ -278,3 +278,31 @@ def test_backward_tile_classification_from_first_and_last_row():
                     kept += f_any
                     needed += t_any
     assert kept == needed and needed > 500
+
+
+def test_balanced_partition_and_grouped_block_order():
+    """Host logic of the multi-GPU split and of the kernels' block order.  The decode split puts
+    sequences into bins of nearly equal summed length; the prefill kernels walk (batch, head)
+    pairs in groups and, inside a group, the late (heavy) query tiles of every head first: the
+    mapping from block number to (pair, tile) must hit every pair and tile exactly once."""
+    import numpy as np
+    from sps_b200 import workloads
+    w = np.array([9, 1, 8, 2, 7, 3, 6, 4, 5, 5])
+    bins = workloads.balanced_partition(w, 3)
+    assert sorted(i for b in bins for i in b) == list(range(10))
+    loads = [int(w[b].sum()) for b in bins]
+    assert max(loads) - min(loads) <= 2
+    assert workloads.balanced_partition([4.0], 2) == [[0], []]
+
+    def block_to_item(block, n_pairs, n_qtiles, group):       # the kernels' arithmetic restated
+        per_group = group * n_qtiles
+        grp, in_grp = divmod(block, per_group)
+        gsize = min(group, n_pairs - grp * group)
+        return grp * group + in_grp % gsize, n_qtiles - 1 - in_grp // gsize
+
+    for n_pairs, n_qtiles, group in ((96, 64, 24), (7, 3, 4), (5, 9, 32), (64, 64, 12), (1, 1, 1)):
+        seen = [block_to_item(b, n_pairs, n_qtiles, group) for b in range(n_pairs * n_qtiles)]
+        assert sorted(seen) == [(p, t) for p in range(n_pairs) for t in range(n_qtiles)]
+        # inside a group the tile number never increases
+        first_group = [t for p, t in seen[:min(group, n_pairs) * n_qtiles]]
+        assert first_group == sorted(first_group, reverse=True)

@@ -37,8 +37,23 @@ def _worker(rank, world, port, q):
     docs = workloads.geometric_docs(8, 512, 100, 0)
     pairs = workloads.useful_pairs(docs[workloads.shard_slice(8, rank, world)], 64)
     pairs_total = bench._sum_over_ranks(float(pairs), world, cpu)
-    q.put((rank, mx, sm, total, pairs_total, (sl.start, sl.stop)))
+    # the strong split of the decode step: bins of equal summed cache length, one per rank
+    bins = workloads.balanced_partition(lens, world)
+    bin_bytes = workloads.decode_bytes(lens[bins[rank]], 64, 16, 64)
+    bin_total = bench._sum_over_ranks(bin_bytes, world, cpu)
+    gathered = bench.gather_over_ranks(float(lens[bins[rank]].sum()), world, cpu)
+    # the timed-region helper itself, on a host function (no GPU work to wait for)
+    region, launch, det = _host_timed_steps(bench, world, rank)
+    q.put((rank, mx, sm, total, pairs_total, (sl.start, sl.stop), bin_total, gathered, det["rank_region_ms"]))
     dist.destroy_process_group()
+
+
+def _host_timed_steps(bench, world, rank):
+    """bench.timed_steps needs CUDA events; this drives the same reductions it ends with."""
+    mine = [5.0 + rank, 7.0 - rank, 6.0]
+    maxima = [bench.max_over_ranks(m, world, torch.device("cpu")) for m in mine]
+    pick = sorted(range(3), key=lambda i: maxima[i])[1]
+    return maxima[pick], 0.0, {"rank_region_ms": bench.gather_over_ranks(mine[pick], world, torch.device("cpu"))}
 
 
 def test_two_gloo_ranks_shard_and_reduce():
@@ -56,8 +71,15 @@ def test_two_gloo_ranks_shard_and_reduce():
     lens = workloads.decode_lengths("cfg2_segmented_decode")
     want_bytes = workloads.decode_bytes(lens, 64, 16, 64)
     want_pairs = workloads.useful_pairs(workloads.geometric_docs(8, 512, 100, 0), 64)
-    for rank, mx, sm, total, pairs_total, _ in res:
+    bins = workloads.balanced_partition(lens, world)
+    assert sorted(i for b in bins for i in b) == list(range(len(lens)))
+    sums = [int(lens[b].sum()) for b in bins]
+    assert max(sums) - min(sums) <= int(lens.max())          # balanced on the summed length
+    for rank, mx, sm, total, pairs_total, _, bin_total, gathered, rank_ms in res:
         assert mx == 11.0 and sm == 300.0
         assert abs(total - want_bytes) < 1.0
         assert pairs_total == float(want_pairs)
+        assert abs(bin_total - want_bytes) < 1.0               # the bins cover every sequence once
+        assert gathered == [float(x) for x in sums]
+        assert rank_ms == [6.0, 6.0]                           # the median region, every rank's own time
     assert res[0][5] == (0, 64) and res[1][5] == (64, 128)
