@@ -48,6 +48,7 @@ struct BwdParams {
   const int* mono;
   int B, H, N;
   int n_xtiles;          // stationary tiles per (batch, head)
+  int group_heads;       // (batch, head) pairs whose operands share L2 at a time
   MaskParams mask;
   float scale_log2;
   float sm_scale;
@@ -171,8 +172,15 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
-  const int bh = blockIdx.x / prm.n_xtiles;
-  const int xt_raw = blockIdx.x % prm.n_xtiles;
+  // (batch, head) pairs go in groups whose operands fit L2 together; inside a group the heavy
+  // tiles of all its heads come first, so the launch ends on light blocks
+  const int gh = prm.group_heads > 0 ? prm.group_heads : 1;
+  const int per_group = gh * prm.n_xtiles;
+  const int grp = blockIdx.x / per_group;
+  const int in_grp = blockIdx.x - grp * per_group;
+  const int gsize = min(gh, prm.B * prm.H - grp * gh);
+  const int bh = grp * gh + in_grp % gsize;
+  const int xt_raw = in_grp / gsize;
   const int b = bh / prm.H;
   const int h = bh - b * prm.H;
   const int ks = prm.mask.ks;

@@ -574,6 +574,15 @@ int spsattn_prefill_bwd_strided(const void* q, const void* k, const void* v, con
   set_out(0, dk, sx[6]);
   set_out(1, dv, sx[7]);
   prm.n_xtiles = mask.ks * ((N / mask.ks + 127) / 128);
+  {
+    // heads whose q, k, v, dO (4 * N * D * 2 bytes each) share about 48 MB of L2 at a time
+    const long long op_bytes = 8LL * N * D;
+    const long long gh = (48LL << 20) / (op_bytes > 0 ? op_bytes : 1);
+    prm.group_heads = (int)(gh < 1 ? 1 : (gh > 32 ? 32 : gh));
+#ifdef SPSATTN_NO_GROUP
+    prm.group_heads = 1;
+#endif
+  }
   if (D == 64)
     rc = fp16 ? launch_prefill_bwd<64, true, kBwdDKV>(ks_map, vs_map, q64, do64, prm, st)
               : launch_prefill_bwd<64, false, kBwdDKV>(ks_map, vs_map, q64, do64, prm, st);
