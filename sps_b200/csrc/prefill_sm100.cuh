@@ -61,6 +61,12 @@ constexpr int kTileM = 128;      // query rows per block
 constexpr int kTileN = 64;       // key tokens per tile
 constexpr int kPrefillThreads = 192;
 
+#ifndef SPSATTN_P_SPLIT
+#define SPSATTN_P_SPLIT_DEFAULT 1
+#else
+#define SPSATTN_P_SPLIT_DEFAULT (SPSATTN_P_SPLIT != 0)
+#endif
+
 template <int D>
 struct PrefillCfg {
   static constexpr int kStagesK = 2;
@@ -72,7 +78,7 @@ struct PrefillCfg {
   static constexpr int kQSubBytes = kTileM * 128;              // 128 rows x 64 elements
   static constexpr int kKVBytes = kTileN * D * 2;              // one K or V tile
   static constexpr int kKVSubBytes = kTileN * 128;             // 64 rows x 64 elements
-  static constexpr int kPBytes = kTileM * kTileN * 2;
+  static constexpr int kPBytes = (D == 64 && SPSATTN_P_SPLIT_DEFAULT) ? 0 : kTileM * kTileN * 2;
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = kOffQ + kQBytes;
   static constexpr int kOffV = kOffK + kStagesK * kKVBytes;
@@ -87,6 +93,15 @@ struct PrefillCfg {
   // tensor pipe runs in issue order.  (With the single accumulator of head_dim 64 the next Q K^T
   // would have to wait for P V; measured slower there.)
   static constexpr bool kPTmem = (D == 128);
+  // head_dim 64: P also lives in tensor memory, but in 32 columns of its own (a second, small
+  // allocation: 128 + 32 columns per block, three blocks per SM = 480 of 512), so the next Q K^T
+  // does not have to wait for this tile's P V.  No shared-memory stores, no swizzle arithmetic,
+  // no proxy fence; the P tile's 16 KB of shared memory are not needed.
+#ifndef SPSATTN_P_SPLIT
+#define SPSATTN_P_SPLIT 1
+#endif
+  static constexpr bool kPSplit = (D == 64) && (SPSATTN_P_SPLIT != 0);
+  static constexpr uint32_t kPCols = kTileN / 2;
 };
 
 struct TileInfo {
@@ -141,6 +156,20 @@ __device__ __forceinline__ TileInfo get_tile(const BlockPlan& bp, const int* tab
 
 constexpr float kRescaleLog2 = 8.0f;
 
+// How the four softmax warps signal the MMA warp: one arrival per warp (lane 0, after the warp has
+// converged, which also orders the other lanes' writes before it) instead of one per thread: 128
+// arrivals on one shared-memory word serialise, twice per tile.
+#ifdef SPSATTN_ARRIVE_ALL
+constexpr int kSoftmaxArrivals = 128;
+__device__ __forceinline__ void softmax_arrive(uint32_t bar, int) { mbar_arrive(bar); }
+#else
+constexpr int kSoftmaxArrivals = 4;
+__device__ __forceinline__ void softmax_arrive(uint32_t bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+#endif
+
 template <int D, bool FP16>
 __global__ void __launch_bounds__(kPrefillThreads, PrefillCfg<D>::kBlocksPerSM)
 prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -150,6 +179,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __shared__ BlockPlan s_plan;
   __shared__ int s_tiles[kTileTable];
   __shared__ uint32_t s_tmem_base;
+  __shared__ uint32_t s_tmem_p;
   __shared__ int s_abort;
 
   const int tid = threadIdx.x;
@@ -227,9 +257,9 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_init(bar_v_full + 8 * s, 1);
         mbar_init(bar_v_empty + 8 * s, 1);
         mbar_init(bar_s_full + 8 * s, 1);
-        mbar_init(bar_s_free + 8 * s, 128);
+        mbar_init(bar_s_free + 8 * s, kSoftmaxArrivals);
       }
-      mbar_init(bar_p_full, 128);
+      mbar_init(bar_p_full, kSoftmaxArrivals);
       mbar_init(bar_pv_done, 1);
       fence_barrier_init();
       // the Q tile depends on nothing but the block index: start it before the plan is known
@@ -242,6 +272,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     __syncwarp();
     tmem_alloc<Cfg::kTmemCols>(smem_u32(&s_tmem_base));
+    if constexpr (Cfg::kPSplit) tmem_alloc<Cfg::kPCols>(smem_u32(&s_tmem_p));
     tmem_relinquish();
   }
   tc_fence_before();
@@ -249,6 +280,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   tc_fence_after();
 
   const uint32_t tmem = s_tmem_base;
+  const uint32_t tmem_p = Cfg::kPSplit ? s_tmem_p : 0u;
   const int n_tiles = s_plan.n_tiles;
   for (int j = tid; j < min(n_tiles, kTileTable); j += kPrefillThreads)
     s_tiles[j] = pack_tile(tile_info(s_plan, j));
@@ -361,9 +393,9 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           const uint32_t od = tmem + Cfg::kColO;
           if (elect_one()) {
             // P: K-major, one 64-key sub-tile; V: MN-major, 16 key rows = 2048 bytes per step
-            if constexpr (Cfg::kPTmem) {
+            if constexpr (Cfg::kPTmem || Cfg::kPSplit) {
               // A from tensor memory: 16 keys = 8 packed columns per step
-              const uint32_t pa = tmem + (j % Cfg::kSBufs) * kTileN;
+              const uint32_t pa = Cfg::kPSplit ? tmem_p : tmem + (j % Cfg::kSBufs) * kTileN;
 #pragma unroll
               for (int kk = 0; kk < kTileN / 16; ++kk)
                 umma_ts(od, pa + 8 * kk, vb0 + ((kk * 2048) >> 4), dv_hi, idesc_pv, j > 0 || kk > 0);
@@ -435,7 +467,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         }
         tc_fence_before();
-        mbar_arrive(bar_s_free + 8 * sb);
+        softmax_arrive(bar_s_free + 8 * sb, lane);
         if (tid == 0) SPS_TRACE(j, 2);
 
         if (t.masked) {
@@ -556,7 +588,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // after the last product that read these columns, in issue order), so there the wait comes
         // after the P write; it is still made for every tile: a parity wait is only meaningful for
         // a waiter that has consumed every earlier phase of the barrier.
-        if (!Cfg::kPTmem && j > 0) {
+        if (!Cfg::kPTmem && j > 0) {      // also the columns of a P of its own (kPSplit)
           if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag, prm.status)) {
             ok = false;
             break;
@@ -569,10 +601,14 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int q8 = 0; q8 < kTileN / 16; ++q8)
             tmem_st8(tmem + lane_addr + sb * kTileN + 8 * q8, pk + 8 * q8);
         }
+        if constexpr (Cfg::kPSplit) {
+          tmem_st16(tmem_p + lane_addr, pk);
+          tmem_st16(tmem_p + lane_addr + 16, pk + 16);
+        }
         // P -> shared memory, K-major 128B-swizzled: 16-byte chunk ch of row r sits at
         // r * 128 + ((ch ^ (r & 7)) << 4) of the [128 x 64] tile
 #pragma unroll
-        for (int ch = 0; ch < (Cfg::kPTmem ? 0 : 8); ++ch) {
+        for (int ch = 0; ch < ((Cfg::kPTmem || Cfg::kPSplit) ? 0 : 8); ++ch) {
           const uint32_t addr = sP + row * 128 + ((ch ^ (row & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[ch * 4]),
                        "r"(pk[ch * 4 + 1]), "r"(pk[ch * 4 + 2]), "r"(pk[ch * 4 + 3])
@@ -599,10 +635,10 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           tmem_wait_st();
         }
         if (tid == 0) SPS_TRACE(j, 7);
-        if constexpr (Cfg::kPTmem) tmem_wait_st();
+        if constexpr (Cfg::kPTmem || Cfg::kPSplit) tmem_wait_st();
         else fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(bar_p_full);
+        softmax_arrive(bar_p_full, lane);
         if (tid == 0) SPS_TRACE(j, 8);
       }
 
@@ -654,6 +690,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (warp == 4) {
     tc_fence_after();
     tmem_dealloc<Cfg::kTmemCols>(tmem);
+    if constexpr (Cfg::kPSplit) tmem_dealloc<Cfg::kPCols>(tmem_p);
   }
 }
 
