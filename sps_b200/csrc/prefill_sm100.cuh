@@ -221,15 +221,20 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   if (tid == 0) {
     // a failure reported by an earlier block turns every later block into a no-op
-    s_abort = (prm.status != nullptr && *reinterpret_cast<volatile int*>(prm.status) != 0) ? 1 : 0;
-    BlockPlan bp;
-    bp.general_docs = (has_docs && prm.mono != nullptr && prm.mono[b] == 0) ? 1 : 0;
+    // the four global words the plan needs are asked for together (the document starts are read
+    // whether or not the ids turn out monotone: the table exists whenever ids were given)
+    const int st_word = prm.status != nullptr ? *reinterpret_cast<volatile int*>(prm.status) : 0;
+    const int mono_b = (has_docs && prm.mono != nullptr) ? prm.mono[b] : 1;
     int lo0 = 0, lo1 = 0;
-    if (has_docs && !bp.general_docs) {
+    if (has_docs && prm.lo != nullptr) {
       const int i1 = min(i0 + kTileM - 1, prm.N - 1);
       lo0 = prm.lo[(size_t)b * prm.N + i0];
       lo1 = prm.lo[(size_t)b * prm.N + i1];
     }
+    s_abort = st_word != 0 ? 1 : 0;
+    BlockPlan bp;
+    bp.general_docs = mono_b == 0 ? 1 : 0;
+    if (bp.general_docs) lo0 = lo1 = 0;
     if (prm.mask.ks == 1) {
       bp.n_streams = 1;
       bp.stream_id[0] = 0;
@@ -282,6 +287,16 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t tmem = s_tmem_base;
   const uint32_t tmem_p = Cfg::kPSplit ? s_tmem_p : 0u;
   const int n_tiles = s_plan.n_tiles;
+  if (warp == 4 && n_tiles > 0 && s_abort == 0) {
+    // the first K tile goes out as soon as the plan is known, before the tile table is built
+    const TileInfo t = tile_info(s_plan, 0);
+    if (elect_one()) {
+      mbar_arrive_expect_tx(bar_k_full, Cfg::kKVBytes);
+      for (int c = 0; c < D / 64; ++c)
+        tma_load_5d(sK + c * Cfg::kKVSubBytes, &tm_k, bar_k_full, c * 64, t.stream, t.k0, h, b);
+    }
+    __syncwarp();
+  }
   for (int j = tid; j < min(n_tiles, kTileTable); j += kPrefillThreads)
     s_tiles[j] = pack_tile(tile_info(s_plan, j));
   __syncthreads();
@@ -328,7 +343,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           if (lane == 0) SPS_TRACE(j, 14);
           return true;
         };
-        bool ok = load_k(0);
+        bool ok = true;   // K tile 0 is on its way already
         for (int j = 0; ok && j < n_tiles; ++j) {
           if (j + 1 < n_tiles) ok = load_k(j + 1);
           if (ok) ok = load_v(j);
