@@ -37,7 +37,7 @@ PREFILL_FULL_WINDOW = "cfg4_full_window"
 GENERATION = "cfg3_xl_generation"
 # DRAM traffic per full-size launch, from ncu captures of a smaller case scaled by the units
 # processed (traffic is proportional to batch rows / sequences)
-PREFILL_DRAM_BYTES_PER_LAUNCH = 2 * (151.4e6 + 33.3e6)
+PREFILL_DRAM_BYTES_PER_LAUNCH = 2 * (151.6e6 + 32.6e6)
 DECODE_DRAM_BYTES_PER_LAUNCH = 4 * (332.2e6 + 4.9e6)
 # head_dim 128 forward: ncu dram bytes of a 4-head launch (quarter of the heads) x4
 FULL_WINDOW_DRAM_BYTES_PER_LAUNCH = 4 * (100.7e6 + 15.4e6)

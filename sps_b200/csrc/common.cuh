@@ -33,6 +33,17 @@ __device__ __forceinline__ float ex2_ordered(float x) {
   return y;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute
+// may start while the kernel before it in the stream is still running; it must execute
+// grid_dependency_wait() before it touches anything that kernel writes (a no-op when the launch
+// carried no such attribute).  The earlier kernel calls grid_launch_dependents() to allow that.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // max of three (one instruction on sm_100)
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;

@@ -25,6 +25,9 @@ doc_prepass_kernel(const void* docs, int is_i64, int64_t stride_b, int64_t strid
   const int b = blockIdx.x;
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
+  // the attention kernel behind this one may be launched as a programmatic dependent: let its
+  // blocks take the free SMs now (it waits for this grid before it reads lo / mono)
+  grid_launch_dependents();
   const uint8_t* base =
       reinterpret_cast<const uint8_t*>(docs) + (size_t)b * stride_b * (is_i64 ? 8 : 4);
   if (tid == 0) {

@@ -221,6 +221,10 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   if (tid == 0) {
     // a failure reported by an earlier block turns every later block into a no-op
+    // launched as a programmatic dependent of the document pre-pass: everything above (and the
+    // other warps' barrier set-up, Q load and tensor-memory allocation) ran beside it; its
+    // outputs are read from here on
+    grid_dependency_wait();
     // the four global words the plan needs are asked for together (the document starts are read
     // whether or not the ids turn out monotone: the table exists whenever ids were given)
     const int st_word = prm.status != nullptr ? *reinterpret_cast<volatile int*>(prm.status) : 0;
@@ -283,6 +287,7 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dependency_wait();   // every thread that reads the pre-pass outputs (thread 0 is past it)
 
   const uint32_t tmem = s_tmem_base;
   const uint32_t tmem_p = Cfg::kPSplit ? s_tmem_p : 0u;

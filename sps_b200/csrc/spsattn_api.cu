@@ -129,8 +129,27 @@ int launch_prefill_sm100(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   if (attr_err != cudaSuccess) return (int)attr_err;
   const long long blocks = (long long)prm.n_qtiles * prm.B * prm.H;
   if (blocks <= 0 || blocks > 0x7fffffffLL) return SPSATTN_ERR_TOO_LARGE;
-  prefill_sm100_kernel<D, FP16><<<(unsigned)blocks, kPrefillThreads, Cfg::kSmemBytes, st>>>(tq, tk, tv, prm);
-  return (int)cudaGetLastError();
+  // With document ids the kernel just before this one in the stream is the pre-pass (8 blocks of
+  // a few microseconds): launched as its programmatic dependent, the attention blocks set up
+  // their barriers, tensor memory and Q tile beside it and wait for it only before they read its
+  // outputs.  Without ids the launch is an ordinary one (whatever precedes it may produce Q, K, V).
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(kPrefillThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+#ifdef SPSATTN_NO_PDL
+  cfg.numAttrs = 0;         // tuning builds: ordinary launch
+#else
+  cfg.numAttrs = prm.lo != nullptr ? 1 : 0;
+#endif
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, prefill_sm100_kernel<D, FP16>, tq, tk, tv, prm);
+  return le != cudaSuccess ? (int)le : (int)cudaGetLastError();
 }
 
 // Persistent launch: two blocks per SM draw the (batch, head, query tile) items from
