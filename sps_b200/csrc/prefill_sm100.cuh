@@ -219,15 +219,17 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   const bool has_docs = prm.docs != nullptr;
 
-  if (tid == 0) {
-    // a failure reported by an earlier block turns every later block into a no-op
-    // launched as a programmatic dependent of the document pre-pass: everything above (and the
-    // other warps' barrier set-up, Q load and tensor-memory allocation) ran beside it; its
-    // outputs are read from here on
+  if (tid == 0 || tid == 32) {
+    // Two planner threads, one per key stream (thread 0: the persistent stream, which holds the
+    // diagonal; thread 32: the other parity).  Launched as a programmatic dependent of the document
+    // pre-pass, the block has run up to here (and its producer warp sets up barriers, the Q load
+    // and tensor memory) beside that kernel; its outputs are read from here on.
     grid_dependency_wait();
-    // the four global words the plan needs are asked for together (the document starts are read
+    const int slot = tid >> 5;
+    // the global words the plan needs are asked for together (the document starts are read
     // whether or not the ids turn out monotone: the table exists whenever ids were given)
-    const int st_word = prm.status != nullptr ? *reinterpret_cast<volatile int*>(prm.status) : 0;
+    int st_word = 0;
+    if (slot == 0 && prm.status != nullptr) st_word = *reinterpret_cast<volatile int*>(prm.status);
     const int mono_b = (has_docs && prm.mono != nullptr) ? prm.mono[b] : 1;
     int lo0 = 0, lo1 = 0;
     if (has_docs && prm.lo != nullptr) {
@@ -235,27 +237,21 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       lo0 = prm.lo[(size_t)b * prm.N + i0];
       lo1 = prm.lo[(size_t)b * prm.N + i1];
     }
-    s_abort = st_word != 0 ? 1 : 0;
-    BlockPlan bp;
-    bp.general_docs = mono_b == 0 ? 1 : 0;
-    if (bp.general_docs) lo0 = lo1 = 0;
-    if (prm.mask.ks == 1) {
-      bp.n_streams = 1;
-      bp.stream_id[0] = 0;
-      bp.stream_id[1] = 0;
-      bp.sp[0] = plan_stream(prm.mask, i0, lo0, lo1, 0, kTileN);
-      bp.sp[1] = bp.sp[0];
-      bp.sp[1].ntiles = 0;
-    } else {
-      bp.n_streams = 2;
-      bp.stream_id[0] = prm.mask.pp;       // persistent stream first: holds the diagonal
-      bp.stream_id[1] = 1 - prm.mask.pp;
-      bp.sp[0] = plan_stream(prm.mask, i0, lo0, lo1, bp.stream_id[0], kTileN);
-      bp.sp[1] = plan_stream(prm.mask, i0, lo0, lo1, bp.stream_id[1], kTileN);
+    SPS_TRACE(3 + 8 * slot, 15);
+    if (mono_b == 0) lo0 = lo1 = 0;
+    const bool two = prm.mask.ks != 1;
+    const int stream = two ? (slot == 0 ? prm.mask.pp : 1 - prm.mask.pp) : 0;
+    StreamPlan sp = plan_stream(prm.mask, i0, lo0, lo1, stream, kTileN);
+    if (!two && slot == 1) sp.ntiles = 0;
+    s_plan.sp[slot] = sp;
+    s_plan.stream_id[slot] = stream;
+    if (slot == 0) {
+      // a failure reported by an earlier block turns every later block into a no-op
+      s_abort = st_word != 0 ? 1 : 0;
+      s_plan.general_docs = mono_b == 0 ? 1 : 0;
+      s_plan.n_streams = two ? 2 : 1;
     }
-    bp.n_tiles = bp.sp[0].ntiles + bp.sp[1].ntiles;
-    s_plan = bp;
-
+    SPS_TRACE(4 + 8 * slot, 15);
   }
   if (warp == 4) {
     if (lane == 0) {
@@ -278,20 +274,23 @@ prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tma_load_4d(sQ + c * Cfg::kQSubBytes, &tm_q, bar_q_full, c * 64, i0, h, b);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
+      SPS_TRACE(5, 15);
     }
     __syncwarp();
     tmem_alloc<Cfg::kTmemCols>(smem_u32(&s_tmem_base));
     if constexpr (Cfg::kPSplit) tmem_alloc<Cfg::kPCols>(smem_u32(&s_tmem_p));
     tmem_relinquish();
+    if (lane == 0) SPS_TRACE(6, 15);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (tid == 0) SPS_TRACE(7, 15);
   grid_dependency_wait();   // every thread that reads the pre-pass outputs (thread 0 is past it)
 
   const uint32_t tmem = s_tmem_base;
   const uint32_t tmem_p = Cfg::kPSplit ? s_tmem_p : 0u;
-  const int n_tiles = s_plan.n_tiles;
+  const int n_tiles = s_plan.sp[0].ntiles + s_plan.sp[1].ntiles;
   if (warp == 4 && n_tiles > 0 && s_abort == 0) {
     // the first K tile goes out as soon as the plan is known, before the tile table is built
     const TileInfo t = tile_info(s_plan, 0);
