@@ -90,6 +90,15 @@ struct BwdCfg {
   static constexpr uint32_t kColAcc0 = kSBufs * kSBufCols, kColAcc1 = kColAcc0 + D;
   static constexpr uint32_t kTmemCols = (D == 64) ? 256 : 512;
   static constexpr int kBlocksPerSM = (D == 64) ? 2 : 1;
+  // dQ at head_dim 64 leaves 64 of the block's 256 columns unused (no second accumulator): dS gets
+  // 32 of them for itself instead of lying over the dP columns, so the products of the next tile
+  // are issued as soon as the softmax warps have read this tile's S / dP, not after this tile's
+  // accumulation (0 restores the shared columns)
+#ifndef SPSATTN_BWD_DS_OWN
+#define SPSATTN_BWD_DS_OWN 1
+#endif
+  static constexpr bool kDsOwn = (MODE == kBwdDQ) && D == 64 && kWGs == 1 && kPTmem && (SPSATTN_BWD_DS_OWN != 0);
+  static constexpr uint32_t kColDsOwn = kColAcc0 + D;
 };
 
 // delta[b, h, i] = sum_d dO * O, rows addressed with each operand's own strides: D / 8 threads
@@ -433,7 +442,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
       for (int j = 0; ok && j < n_tiles; ++j) {
         // with P / dS laid over a single S / dP pair the next products may only be issued after this
         // tile's accumulation (the tensor pipe runs in issue order)
-        constexpr bool kAhead = !(Cfg::kPTmem && Cfg::kSBufs == 1);
+        constexpr bool kAhead = !(Cfg::kPTmem && Cfg::kSBufs == 1) || Cfg::kDsOwn;
         if (kAhead && j + 1 < n_tiles) ok = issue_s(j + 1);
         if (!ok) break;
         const int st = j % Cfg::kStages;
@@ -449,9 +458,10 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           if constexpr (Cfg::kPTmem) {
             // A from tensor memory: 16 contraction elements = 8 columns per step
             const uint32_t ta = tmem + g * Cfg::kSBufCols;
+            const uint32_t a_ds = Cfg::kDsOwn ? tmem + Cfg::kColDsOwn : ta + Cfg::kColDP;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
-              umma_ts(tmem + Cfg::kColAcc0, ta + Cfg::kColDP + 8 * kk, y0 + ((kk * 2048) >> 4), dym_hi, idesc_acc,
+              umma_ts(tmem + Cfg::kColAcc0, a_ds + 8 * kk, y0 + ((kk * 2048) >> 4), dym_hi, idesc_acc,
                       !(j == 0 && kk == 0));
             if constexpr (kDKV) {
 #pragma unroll
@@ -580,7 +590,9 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
           ok = false;
           break;
         }
-        if (jl > 0) {   // this warpgroup's P / dS tiles are free once its previous accumulation is done
+        // this warpgroup's P / dS tiles are free once its previous accumulation is done (with dS in
+        // columns of its own the wait comes later, before the first dS store)
+        if (!Cfg::kDsOwn && jl > 0) {
           if (!mbar_wait(bar_acc_done + 8 * wg, (jl - 1) & 1, abort_flag, prm.status)) {
             ok = false;
             break;
@@ -689,12 +701,20 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
             pk_ds[e / 2] = pack2<FP16>(ds.x, ds.y);
           }
           if constexpr (Cfg::kPTmem) {
+            if (Cfg::kDsOwn && chunk == 0 && jl > 0) {
+              // on a failed wait the tile is finished anyway (its stores are harmless) and the
+              // loop ends below
+              if (!mbar_wait(bar_acc_done + 8 * wg, (jl - 1) & 1, abort_flag, prm.status)) ok = false;
+              tc_fence_after();
+            }
             // over the columns of S / dP this warp has already read: chunk c (CH columns of each)
             // leaves CH / 2 packed columns of P at S + c * CH / 2 and of dS at dP + c * CH / 2
+            // (dS at its own columns in the dQ kernel of head_dim 64)
+            const uint32_t ds_to = Cfg::kDsOwn ? tmem + lane_addr + Cfg::kColDsOwn : ts + Cfg::kColDP;
 #pragma unroll
             for (int q8 = 0; q8 < CH / 16; ++q8) {
               if constexpr (kDKV) tmem_st8(ts + Cfg::kColS + chunk * (CH / 2) + 8 * q8, pk_p + 8 * q8);
-              tmem_st8(ts + Cfg::kColDP + chunk * (CH / 2) + 8 * q8, pk_ds + 8 * q8);
+              tmem_st8(ds_to + chunk * (CH / 2) + 8 * q8, pk_ds + 8 * q8);
             }
           }
           // K-major 128B-swizzled [128 x 64] tiles: 16-byte chunk ch of row r sits at
@@ -715,6 +735,7 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         }
         if constexpr (Cfg::kPTmem) tmem_wait_st();
         else fence_proxy_async_smem();
+        if (!ok) break;
         tc_fence_before();
         mbar_arrive(bar_p_full + 8 * wg);
         if constexpr (kDKV) {
