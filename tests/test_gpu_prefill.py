@@ -240,6 +240,39 @@ def test_full_size_properties_and_spot_rows():
         _check(out[b:b + 1, h:h + 1][:, :, torch.from_numpy(rows).to(out.device)], ref)
 
 
+def test_prefill_with_documents_replays_from_a_cuda_graph():
+    """With document ids the attention kernel is launched as a programmatic dependent of the
+    pre-pass.  The pair must survive stream capture: two captured calls, replayed twice, give the
+    eager result bit for bit, and back-to-back eager calls on a side stream do too."""
+    import sps_b200
+    from sps_b200 import workloads
+    wl = workloads.make_prefill("cfg1_s_scale", _dev(), batch_slice=slice(0, 2), head_slice=slice(0, 4))
+    ref = torch.empty_like(wl.q)
+    out = torch.empty_like(wl.q)
+
+    def call(o):
+        return sps_b200.prefill_attention(wl.q, wl.k, wl.v, wl.sm_scale, persistent_parity=0,
+                                          temporary_window=wl.window, documents_idx=wl.docs, out=o)
+    call(ref)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        call(out)
+        call(out)
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref)
+    out.zero_()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        call(out)
+        call(out)
+    graph.replay()
+    graph.replay()
+    torch.cuda.synchronize()
+    sps_b200.check_device_status()
+    assert torch.equal(out, ref)
+
+
 def test_full_window_config_spot_rows():
     """[.,.,8192,128], w = 4096, one document: the least sparse mask (head-sharded in the bench)."""
     import sps_b200
