@@ -318,6 +318,63 @@ def reference_triton(device):
     except Exception as e:
         out[DECODE] = {"unavailable": f"unavailable on this box: {e!r}"}
     torch.cuda.empty_cache()
+    # the reference's fused cache update (one Triton launch) against this repository's, on cfg2's
+    # cache shapes: the same ten updates on two copies of the caches, contents compared bit for bit
+    try:
+        from modeling.models.utils.decode_attention_fast import fused_sps_kv_update as ref_update
+        S, H, D, ring, _, cap = workloads.DECODE_CONFIGS[DECODE]
+        g = torch.Generator(device="cpu").manual_seed(0)
+        bf = torch.bfloat16
+
+        def caches():
+            gg = torch.Generator(device="cpu").manual_seed(1)
+            return dict(
+                nw_k=torch.zeros(S, H, ring, D, dtype=bf, device=device), nw_v=torch.zeros(S, H, ring, D, dtype=bf, device=device),
+                nw_len=torch.full((S,), ring, dtype=torch.int64, device=device),
+                nw_pos=torch.randint(0, ring, (S,), generator=gg).to(device),
+                br_k=torch.zeros(S, H, cap, D, dtype=bf, device=device), br_v=torch.zeros(S, H, cap, D, dtype=bf, device=device),
+                br_len=torch.randint(512, cap - 64, (S, 1), generator=gg).expand(S, H).contiguous().to(device))
+        new = [torch.randn(S, H, D, generator=g).to(bf).to(device) for _ in range(4)]
+        active = torch.ones(S, dtype=torch.bool, device=device)
+        step = dict(k_window_BxHxD=new[0], v_window_BxHxD=new[1], k_retained_BxHxD=new[2], v_retained_BxHxD=new[3],
+                    active_mask_B=active, window_tokens=ring)
+        timings = {}
+        state = {}
+        for tag, fn in (("reference", ref_update), ("ours", sps_b200.fused_sps_kv_update)):
+            c = caches()
+            fn(**c, **step)                       # warm-up (and the Triton compile)
+            c = caches()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                fn(**c, **step)
+            e1.record()
+            torch.cuda.synchronize()
+            timings[tag] = e0.elapsed_time(e1) / 10
+            state[tag] = c
+        # rows (of D elements) that differ between the two sets of caches, and whether this
+        # repository's ring holds the ten new rows in ten consecutive slots from the old position
+        # on, which is what the sequential rule (the reference's unfused methods) gives
+        diff_rows = {k: int((state["reference"][k] != state["ours"][k]).reshape(S * H, -1, D).any(-1).sum())
+                     for k in ("nw_k", "nw_v", "br_k", "br_v")}
+        counters_same = all(torch.equal(state["reference"][k], state["ours"][k]) for k in ("nw_len", "nw_pos", "br_len"))
+        pos0 = caches()["nw_pos"]
+        slots = (pos0[:, None] + torch.arange(10, device=device)[None, :]) % ring
+        filled = state["ours"]["nw_k"].float().abs().sum(-1) != 0                      # [S, H, ring]
+        want = torch.zeros(S, ring, dtype=torch.bool, device=device).scatter_(1, slots, True)
+        out["fused_sps_kv_update"] = {
+            "shape": f"[{S},{H},{D}] new rows into ring {ring} and retained cache {cap}, bf16, 10 updates",
+            "ms": timings["reference"], "ms_this_repo": timings["ours"],
+            "counters_identical": bool(counters_same), "rows_differing": diff_rows,
+            "this_repo_ring_matches_sequential_rule": bool((filled == want[:, None, :]).all()),
+            "note": "where rows differ, the reference's kernel wrote a ring row to the wrong slot: its programs "
+                    "(b, h != 0) read nw_pos while program (b, 0) advances it, with no ordering between them; "
+                    "this repository reads the counters of a sequence in one block before anything is written"}
+        del state
+    except Exception as e:
+        out["fused_sps_kv_update"] = {"unavailable": f"unavailable on this box: {e!r}"}
+    torch.cuda.empty_cache()
     return out
 
 
