@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _reference_path():
     env = os.environ.get("REFERENCE_ROOT")
     cands = [os.path.join(env, "src")] if env else []
-    cands += [os.path.join(ROOT, "baseline", "_ref"), "/root/reference/src"]
+    cands += [os.path.join(ROOT, "baseline", "_ref")]
     for c in cands:
         if os.path.isdir(os.path.join(c, "modeling", "models")):
             return c
