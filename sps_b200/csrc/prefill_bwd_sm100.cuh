@@ -656,6 +656,24 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
         // columns are processed CH at a time; in kDKV mode the per-column constants of a chunk
         // are staged in registers with vector loads before the scores arrive
         constexpr int CH = kDKV ? 16 : 32;
+        // the tensor-memory loads of chunk c + 1 are issued before the arithmetic of chunk c (two
+        // register sets), so only the first load of a tile is waited for at full latency
+#ifdef SPSATTN_BWD_NO_LD_AHEAD
+        constexpr bool kLdAhead = false;
+#else
+        constexpr bool kLdAhead = true;
+#endif
+        uint32_t rsb[kLdAhead ? 2 : 1][CH], rdb[kLdAhead ? 2 : 1][CH];
+        auto ld_chunk = [&](int chunk, uint32_t (&a)[CH], uint32_t (&d)[CH]) {
+          if constexpr (CH == 32) {
+            tmem_ld32(ts + Cfg::kColS + chunk * CH, a);
+            tmem_ld32(ts + Cfg::kColDP + chunk * CH, d);
+          } else {
+            tmem_ld16(ts + Cfg::kColS + chunk * CH, a);
+            tmem_ld16(ts + Cfg::kColDP + chunk * CH, d);
+          }
+        };
+        if constexpr (kLdAhead) ld_chunk(0, rsb[0], rdb[0]);
 #pragma unroll
         for (int chunk = 0; chunk < 64 / CH; ++chunk) {
           float nl_c[kDKV ? CH : 1], dl_c[kDKV ? CH : 1];
@@ -668,15 +686,13 @@ prefill_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid
               dl_c[e] = b4.x, dl_c[e + 1] = b4.y, dl_c[e + 2] = b4.z, dl_c[e + 3] = b4.w;
             }
           }
-          uint32_t rs[CH], rd[CH];
-          if constexpr (CH == 32) {
-            tmem_ld32(ts + Cfg::kColS + chunk * CH, rs);
-            tmem_ld32(ts + Cfg::kColDP + chunk * CH, rd);
-          } else {
-            tmem_ld16(ts + Cfg::kColS + chunk * CH, rs);
-            tmem_ld16(ts + Cfg::kColDP + chunk * CH, rd);
-          }
+          uint32_t (&rs)[CH] = rsb[kLdAhead ? (chunk & 1) : 0];
+          uint32_t (&rd)[CH] = rdb[kLdAhead ? (chunk & 1) : 0];
+          if constexpr (!kLdAhead) ld_chunk(chunk, rs, rd);
           tmem_wait_ld();
+          if constexpr (kLdAhead) {
+            if (chunk + 1 < 64 / CH) ld_chunk(chunk + 1, rsb[(chunk + 1) & 1], rdb[(chunk + 1) & 1]);
+          }
           if (chunk == 64 / CH - 1) {
             tc_fence_before();
             mbar_arrive(bar_s_free + 8 * sb);
